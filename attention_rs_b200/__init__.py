@@ -1,0 +1,25 @@
+"""B200-native paged attention (decode) and reshape_and_cache.
+
+The compute lives in ``libpagedattention_b200.so`` (hand-written CUDA for sm_100a,
+C ABI declared in ``include/pagedattention_b200.h``).  This package is the thin
+host layer over it for Python callers: it mirrors the reference's two public
+operators, ``paged_attention`` and ``reshape_and_cache``
+(src/paged_attention.rs:515-537 and :890-904 of the reference), on torch CUDA
+tensors.  torch is used for device memory and streams only.
+
+There is no CPU path: importing works anywhere, but every operator raises unless
+the shared library is present and the tensors live on a CUDA device.
+"""
+from .ops import (  # noqa: F401
+    PagedAttentionError,
+    library_path,
+    load_library,
+    paged_attention,
+    paged_attention_v1,
+    paged_attention_v2,
+    reshape_and_cache,
+    uses_partitions,
+    workspace_bytes,
+)
+
+__version__ = "0.1.0"

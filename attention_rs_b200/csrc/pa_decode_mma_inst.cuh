@@ -1,0 +1,72 @@
+// Launcher of the tensor-core decode kernel family for one (query dtype, cache
+// kind); included by one small translation unit per combination so the
+// instantiations compile in parallel.
+#pragma once
+
+#include "pa_decode_mma.cuh"
+#include "pa_launch.h"
+
+namespace pa {
+
+template <typename T, bool FP8, int HEAD, int BS>
+int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
+  using C = DecodeCfg<T, FP8, HEAD, BS>;
+  auto kernel = paged_decode_mma_kernel<T, FP8, HEAD, BS>;
+  // Opt in to the large dynamic shared-memory carve-out once per device instead
+  // of on every call (the reference sets it per call, src/kernels/src/pagedattention.cu:570-573).
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return PA_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return PA_ERR_CUDA;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int gsplit = (p.group + 15) / 16;
+  const bool partitioned = p.partition_size > 0;
+  dim3 grid(p.num_kv_heads * gsplit, p.num_seqs, partitioned ? p.max_parts : 1);
+  kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p);
+  if (partitioned) {
+    dim3 mgrid(p.num_heads, p.num_seqs);
+    const size_t msmem = (static_cast<size_t>(p.max_parts) + 4 * HEAD) * sizeof(float);
+    paged_decode_merge_kernel<T, HEAD><<<mgrid, 128, msmem, stream>>>(
+        reinterpret_cast<T*>(p.out), p.exp_sums, p.max_logits, reinterpret_cast<const T*>(p.tmp_out), p.context_lens,
+        p.max_parts, p.partition_size);
+  }
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+template <typename T, bool FP8, int HEAD>
+int launch_decode_mma_head(const DecodeParams& p, int block_size, cudaStream_t stream) {
+  switch (block_size) {
+    case 16: return launch_decode_mma_one<T, FP8, HEAD, 16>(p, stream);
+    case 32: return launch_decode_mma_one<T, FP8, HEAD, 32>(p, stream);
+    case 8:
+      if constexpr (!FP8) return launch_decode_mma_one<T, FP8, HEAD, 8>(p, stream);
+      return PA_ERR_UNSUPPORTED;
+    default: return PA_ERR_UNSUPPORTED;
+  }
+}
+
+// Head sizes are the reference's list (src/paged_attention.rs:108-117,
+// src/kernels/src/pagedattention.cu:635-662); the FP8 path takes those that are
+// multiples of 32.
+template <typename T, bool FP8>
+int launch_decode_mma_impl(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream) {
+  switch (head_size) {
+    case 64: return launch_decode_mma_head<T, FP8, 64>(p, block_size, stream);
+    case 96: return launch_decode_mma_head<T, FP8, 96>(p, block_size, stream);
+    case 128: return launch_decode_mma_head<T, FP8, 128>(p, block_size, stream);
+    case 192: return launch_decode_mma_head<T, FP8, 192>(p, block_size, stream);
+    case 256: return launch_decode_mma_head<T, FP8, 256>(p, block_size, stream);
+    case 80:
+      if constexpr (!FP8) return launch_decode_mma_head<T, FP8, 80>(p, block_size, stream);
+      return PA_ERR_UNSUPPORTED;
+    case 112:
+      if constexpr (!FP8) return launch_decode_mma_head<T, FP8, 112>(p, block_size, stream);
+      return PA_ERR_UNSUPPORTED;
+    default: return PA_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace pa

@@ -1,0 +1,155 @@
+// Generic paged decode attention: any query dtype (f16 / bf16 / f32), any cache
+// dtype (same as the query, or FP8 E4M3), any head size up to 256 and any block
+// size, strides of any alignment.  One CTA per (sequence, query head, partition),
+// one warp per token, lanes across the head dimension, online softmax per warp.
+//
+// This kernel exists for coverage, not speed: it serves the combinations the
+// tensor-core kernel does not take (fp32 tensors, FP8 caches with head sizes that
+// are not multiples of 32 or block size 8, misaligned views).  All arithmetic is
+// fp32, which also makes it the in-library cross-check of the tensor-core kernel.
+// Semantics follow src/kernels/src/pagedattention.cu:92-410 of the reference.
+#pragma once
+
+#include "pa_common.cuh"
+#include "pa_decode_mma.cuh"  // DecodeParams
+
+namespace pa {
+
+template <typename KV>
+__device__ __forceinline__ float kv_to_f32(const KV* base, int64_t idx);
+template <>
+__device__ __forceinline__ float kv_to_f32<float>(const float* b, int64_t i) { return b[i]; }
+template <>
+__device__ __forceinline__ float kv_to_f32<__half>(const __half* b, int64_t i) { return __half2float(b[i]); }
+template <>
+__device__ __forceinline__ float kv_to_f32<__nv_bfloat16>(const __nv_bfloat16* b, int64_t i) { return __bfloat162float(b[i]); }
+template <>
+__device__ __forceinline__ float kv_to_f32<uint8_t>(const uint8_t* b, int64_t i) {
+  const uint32_t h2 = e4m3x2_to_f16x2(b[i]);
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xffffu)));
+}
+
+constexpr int SIMT_WARPS = 4;
+constexpr int SIMT_MAX_PER_LANE = 8;  // head sizes up to 256
+
+template <typename T, typename KV>
+__global__ void __launch_bounds__(SIMT_WARPS * 32)
+paged_decode_simt_kernel(const DecodeParams p, const int head_size, const int block_size) {
+  const int head = blockIdx.x, seq = blockIdx.y, part = blockIdx.z;
+  const int ctx = static_cast<int>(p.context_lens[seq]);
+  const bool partitioned = p.partition_size > 0;
+  int t_begin = 0, t_end = ctx;
+  if (partitioned) {
+    t_begin = part * p.partition_size;
+    if (t_begin >= ctx) return;
+    t_end = min(ctx, t_begin + p.partition_size);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  T* out_row = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head) * head_size;
+  if (ctx == 0) {
+    if (!partitioned)
+      for (int d = threadIdx.x; d < head_size; d += blockDim.x) out_row[d] = from_f32<T>(0.f);
+    return;
+  }
+  constexpr bool FP8 = sizeof(KV) == 1;
+  const int x = 16 / static_cast<int>(sizeof(KV));
+  const int kvh = head / p.group;
+  const float kscale = FP8 ? p.k_scale : 1.f, vscale = FP8 ? p.v_scale : 1.f;
+  const float slope = p.alibi_slopes ? p.alibi_slopes[head] : 0.f;
+  const KV* kc = reinterpret_cast<const KV*>(p.k_cache);
+  const KV* vc = reinterpret_cast<const KV*>(p.v_cache);
+  const T* q = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(seq) * p.q_stride + static_cast<int64_t>(head) * head_size;
+  const uint32_t* table = p.block_tables + static_cast<int64_t>(seq) * p.max_num_blocks_per_seq;
+
+  float qr[SIMT_MAX_PER_LANE], acc[SIMT_MAX_PER_LANE];
+#pragma unroll
+  for (int k = 0; k < SIMT_MAX_PER_LANE; ++k) {
+    const int d = lane + 32 * k;
+    qr[k] = d < head_size ? to_f32<T>(q[d]) : 0.f;
+    acc[k] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int t = t_begin + warp; t < t_end; t += SIMT_WARPS) {
+    const int64_t base = static_cast<int64_t>(table[t / block_size]) * p.kv_block_stride + static_cast<int64_t>(kvh) * p.kv_head_stride;
+    const int off = t % block_size;
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < SIMT_MAX_PER_LANE; ++k) {
+      const int d = lane + 32 * k;
+      if (d < head_size) dot += qr[k] * kv_to_f32<KV>(kc, base + (static_cast<int64_t>(d / x) * block_size + off) * x + d % x);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    float s = dot * (p.scale * kscale);
+    if (p.softcap != 1.0f) s = tanhf(s / p.softcap) * p.softcap;
+    s += slope * static_cast<float>(t - ctx + 1);
+    const float mn = fmaxf(m, s);
+    const float corr = __expf(m - mn), pr = __expf(s - mn);
+    l = l * corr + pr;
+    m = mn;
+#pragma unroll
+    for (int k = 0; k < SIMT_MAX_PER_LANE; ++k) {
+      const int d = lane + 32 * k;
+      if (d < head_size) acc[k] = acc[k] * corr + pr * kv_to_f32<KV>(vc, base + static_cast<int64_t>(d) * block_size + off);
+    }
+  }
+
+  __shared__ float s_m[SIMT_WARPS], s_l[SIMT_WARPS];
+  __shared__ float s_acc[SIMT_WARPS][256];
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+  for (int k = 0; k < SIMT_MAX_PER_LANE; ++k) {
+    const int d = lane + 32 * k;
+    if (d < head_size) s_acc[warp][d] = acc[k];
+  }
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < SIMT_WARPS; ++w) M = fmaxf(M, s_m[w]);
+  float den = 0.f;
+  float wgt[SIMT_WARPS];
+#pragma unroll
+  for (int w = 0; w < SIMT_WARPS; ++w) {
+    wgt[w] = __expf(s_m[w] - M);
+    den += wgt[w] * s_l[w];
+  }
+  const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.max_parts + part;
+  T* dst = partitioned ? reinterpret_cast<T*>(p.tmp_out) + slot * head_size : out_row;
+  for (int d = threadIdx.x; d < head_size; d += blockDim.x) {
+    float num = 0.f;
+#pragma unroll
+    for (int w = 0; w < SIMT_WARPS; ++w) num += wgt[w] * s_acc[w][d];
+    dst[d] = from_f32<T>(num * vscale / den);
+  }
+  if (partitioned && threadIdx.x == 0) {
+    p.max_logits[slot] = M * LOG2E;  // the merge kernel works in the log2 domain
+    p.exp_sums[slot] = den;
+  }
+}
+
+// Head size as a run-time value: merge kernel for the generic path.
+template <typename T>
+__global__ void __launch_bounds__(128)
+paged_decode_merge_generic_kernel(T* __restrict__ out, const float* __restrict__ exp_sums,
+                                  const float* __restrict__ max_logits, const T* __restrict__ tmp_out,
+                                  const uint32_t* __restrict__ context_lens, int max_parts, int partition_size,
+                                  int head_size) {
+  const int head = blockIdx.x, seq = blockIdx.y, num_heads = gridDim.x;
+  const int ctx = static_cast<int>(context_lens[seq]);
+  const int nparts = (ctx + partition_size - 1) / partition_size;
+  T* o = out + (static_cast<int64_t>(seq) * num_heads + head) * head_size;
+  const int64_t slot0 = (static_cast<int64_t>(seq) * num_heads + head) * max_parts;
+  const T* tp = tmp_out + slot0 * head_size;
+  float mx = -INFINITY;
+  for (int j = 0; j < nparts; ++j) mx = fmaxf(mx, max_logits[slot0 + j]);
+  float sum = 0.f;
+  for (int j = 0; j < nparts; ++j) sum += exp_sums[slot0 + j] * exp2f(max_logits[slot0 + j] - mx);
+  for (int d = threadIdx.x; d < head_size; d += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < nparts; ++j)
+      a += exp_sums[slot0 + j] * exp2f(max_logits[slot0 + j] - mx) * to_f32<T>(tp[static_cast<int64_t>(j) * head_size + d]);
+    o[d] = from_f32<T>(nparts > 0 ? a / sum : 0.f);
+  }
+}
+
+}  // namespace pa

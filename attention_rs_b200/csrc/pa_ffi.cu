@@ -1,0 +1,278 @@
+// C ABI of the library: the reference's three FFI symbols, their status-returning
+// "_ex" variants, kernel selection, and the device status word.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "pa_decode_simt.cuh"
+#include "pa_launch.h"
+
+namespace pa {
+
+// ---------------------------------------------------------------- per-thread error text
+
+static thread_local char t_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// ---------------------------------------------------------------- device status word
+
+__device__ unsigned g_status_word = 0u;
+
+unsigned* device_status_word() {
+  static unsigned* cache[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cache[dev] == nullptr) {
+    unsigned* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_status_word) != cudaSuccess) return nullptr;
+    cache[dev] = ptr;
+  }
+  return cache[dev];
+}
+
+// ---------------------------------------------------------------- kernel selection
+
+namespace {
+
+template <typename T, typename KV>
+int launch_simt(const DecodeParams& p, const AttnArgs& a, cudaStream_t stream) {
+  dim3 grid(a.num_heads, a.num_seqs, p.partition_size > 0 ? p.max_parts : 1);
+  paged_decode_simt_kernel<T, KV><<<grid, SIMT_WARPS * 32, 0, stream>>>(p, a.head_size, a.block_size);
+  if (p.partition_size > 0) {
+    dim3 mgrid(a.num_heads, a.num_seqs);
+    paged_decode_merge_generic_kernel<T><<<mgrid, 128, 0, stream>>>(
+        reinterpret_cast<T*>(p.out), p.exp_sums, p.max_logits, reinterpret_cast<const T*>(p.tmp_out), p.context_lens,
+        p.max_parts, p.partition_size, a.head_size);
+  }
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+bool force_simt() {
+  static const int v = [] {
+    const char* e = getenv("PA_FORCE_SIMT");
+    return (e != nullptr && e[0] == '1') ? 1 : 0;
+  }();
+  return v != 0;
+}
+
+}  // namespace
+
+int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
+  if (a.num_seqs <= 0 || a.num_heads <= 0) return PA_OK;
+  if (a.num_kv_heads <= 0 || a.num_heads % a.num_kv_heads != 0)
+    return fail(PA_ERR_INVALID_ARGUMENT, "num_heads (%d) must be a multiple of num_kv_heads (%d)", a.num_heads, a.num_kv_heads);
+  if (a.head_size <= 0 || a.head_size > 256 || a.block_size <= 0)
+    return fail(PA_ERR_UNSUPPORTED, "head_size %d / block_size %d not supported", a.head_size, a.block_size);
+  const int qsize = dtype_size(a.dtype), kvsize = dtype_size(a.kv_dtype);
+  if (qsize == 0 || a.dtype == DT_FP8) return fail(PA_ERR_UNSUPPORTED, "query dtype code %u not supported", a.dtype);
+  if (a.kv_dtype != a.dtype && a.kv_dtype != DT_FP8)
+    return fail(PA_ERR_UNSUPPORTED, "cache dtype code %u not supported with query dtype code %u", a.kv_dtype, a.dtype);
+  if (a.head_size % (16 / kvsize) != 0)
+    return fail(PA_ERR_UNSUPPORTED, "head_size %d is not a multiple of the key-cache chunk width %d", a.head_size, 16 / kvsize);
+
+  DecodeParams p;
+  p.out = a.out;
+  p.exp_sums = a.exp_sums;
+  p.max_logits = a.max_logits;
+  p.tmp_out = a.tmp_out;
+  p.q = a.query;
+  p.k_cache = a.key_cache;
+  p.v_cache = a.value_cache;
+  p.block_tables = a.block_tables;
+  p.context_lens = a.context_lens;
+  p.alibi_slopes = a.alibi_slopes;
+  p.status = device_status_word();
+  if (p.status == nullptr) return fail(PA_ERR_CUDA, "cannot resolve the device status word");
+  p.kv_block_stride = a.kv_block_stride;
+  p.kv_head_stride = a.kv_head_stride;
+  p.num_seqs = a.num_seqs;
+  p.num_heads = a.num_heads;
+  p.num_kv_heads = a.num_kv_heads;
+  p.group = a.num_heads / a.num_kv_heads;
+  p.max_num_blocks_per_seq = a.max_num_blocks_per_seq;
+  p.partition_size = a.partitioned ? PA_PARTITION_SIZE : 0;
+  p.max_parts = a.partitioned ? (a.max_context_len + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE : 1;
+  if (p.max_parts < 1) p.max_parts = 1;
+  p.q_stride = a.q_stride;
+  p.scale = a.scale;
+  p.softcap = a.softcap;
+  p.k_scale = a.k_scale;
+  p.v_scale = a.v_scale;
+
+  // The tensor-core kernel moves whole (block, head) tiles with 16-byte-granular bulk
+  // copies and reads the query in 4-byte words; views that break that go to the generic kernel.
+  const bool aligned = reinterpret_cast<uintptr_t>(a.key_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(a.value_cache) % 16 == 0 &&
+                       (a.kv_block_stride * kvsize) % 16 == 0 && (a.kv_head_stride * kvsize) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(a.query) % 4 == 0 && reinterpret_cast<uintptr_t>(a.out) % 4 == 0 &&
+                       a.q_stride % 2 == 0 && (!a.partitioned || reinterpret_cast<uintptr_t>(a.tmp_out) % 4 == 0);
+  if (qsize == 2 && aligned && !force_simt()) {
+    int rc = PA_ERR_UNSUPPORTED;
+    if (a.dtype == DT_BF16 && a.kv_dtype == DT_BF16) rc = launch_decode_mma_bf16(p, a.head_size, a.block_size, stream);
+    else if (a.dtype == DT_F16 && a.kv_dtype == DT_F16) rc = launch_decode_mma_f16(p, a.head_size, a.block_size, stream);
+    else if (a.dtype == DT_BF16 && a.kv_dtype == DT_FP8) rc = launch_decode_mma_bf16_fp8(p, a.head_size, a.block_size, stream);
+    else if (a.dtype == DT_F16 && a.kv_dtype == DT_FP8) rc = launch_decode_mma_f16_fp8(p, a.head_size, a.block_size, stream);
+    if (rc != PA_ERR_UNSUPPORTED) return rc == PA_OK ? rc : fail(rc, "kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  int rc = PA_ERR_UNSUPPORTED;
+  if (a.dtype == DT_F32 && a.kv_dtype == DT_F32) rc = launch_simt<float, float>(p, a, stream);
+  else if (a.dtype == DT_F16 && a.kv_dtype == DT_F16) rc = launch_simt<__half, __half>(p, a, stream);
+  else if (a.dtype == DT_BF16 && a.kv_dtype == DT_BF16) rc = launch_simt<__nv_bfloat16, __nv_bfloat16>(p, a, stream);
+  else if (a.dtype == DT_F32 && a.kv_dtype == DT_FP8) rc = launch_simt<float, uint8_t>(p, a, stream);
+  else if (a.dtype == DT_F16 && a.kv_dtype == DT_FP8) rc = launch_simt<__half, uint8_t>(p, a, stream);
+  else if (a.dtype == DT_BF16 && a.kv_dtype == DT_FP8) rc = launch_simt<__nv_bfloat16, uint8_t>(p, a, stream);
+  if (rc == PA_ERR_UNSUPPORTED) return fail(rc, "no kernel for query dtype %u / cache dtype %u", a.dtype, a.kv_dtype);
+  return rc == PA_OK ? rc : fail(rc, "kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+}  // namespace pa
+
+// ---------------------------------------------------------------- C entry points
+
+using namespace pa;
+
+extern "C" {
+
+int call_reshape_and_cache_ex(const void* key, const void* value, void* key_cache, void* value_cache,
+                              const int64_t* slot_mapping, int32_t num_tokens, int32_t num_heads, int32_t head_size,
+                              int32_t block_size, int32_t x, int32_t key_stride, int32_t value_stride, uint32_t dtype,
+                              uint32_t cache_dtype, float k_scale, float v_scale, int64_t stream) {
+  if (num_tokens == 0) return PA_OK;
+  if (!key || !value || !key_cache || !value_cache || !slot_mapping)
+    return fail(PA_ERR_INVALID_ARGUMENT, "null pointer passed to reshape_and_cache");
+  if (num_tokens < 0 || num_heads <= 0 || head_size <= 0 || block_size <= 0 || x <= 0 || head_size % x != 0)
+    return fail(PA_ERR_INVALID_ARGUMENT, "bad sizes: tokens %d heads %d head_size %d block_size %d x %d", num_tokens,
+                num_heads, head_size, block_size, x);
+  if (dtype_size(dtype) == 0 || dtype == DT_FP8) return fail(PA_ERR_UNSUPPORTED, "dtype code %u not supported", dtype);
+  if (cache_dtype != dtype && cache_dtype != DT_FP8)
+    return fail(PA_ERR_UNSUPPORTED, "cache dtype code %u not supported with dtype code %u", cache_dtype, dtype);
+  if (cache_dtype == DT_FP8 && !(k_scale > 0.f && v_scale > 0.f))
+    return fail(PA_ERR_INVALID_ARGUMENT, "FP8 cache needs positive k_scale / v_scale");
+  ReshapeArgs a{key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads, head_size, block_size, x,
+                key_stride, value_stride, dtype, cache_dtype, k_scale, v_scale};
+  const int rc = launch_reshape_and_cache(a, reinterpret_cast<cudaStream_t>(stream));
+  return rc == PA_OK ? rc : fail(rc, "reshape_and_cache launch failed (%d)", rc);
+}
+
+void call_reshape_and_cache(void* key, void* value, void* key_cache, void* value_cache, int64_t* slot_mapping,
+                            int32_t num_tokens, int32_t num_heads, int32_t head_size, int32_t block_size, int32_t x,
+                            int32_t key_stride, int32_t value_stride, uint32_t dtype, int64_t stream) {
+  (void)call_reshape_and_cache_ex(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads, head_size,
+                                  block_size, x, key_stride, value_stride, dtype, dtype, 1.f, 1.f, stream);
+}
+
+static int attention_entry(bool partitioned, void* out, float* exp_sums, float* max_logits, void* tmp_out,
+                           const void* query, const void* key_cache, const void* value_cache, int32_t num_kv_heads,
+                           float scale, const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
+                           int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                           int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
+                           int32_t kv_head_stride, uint32_t dtype, float softcapping, const float* alibi_slopes,
+                           uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream) {
+  if (num_seqs == 0) return PA_OK;
+  if (!out || !query || !key_cache || !value_cache || !block_tables || !context_lens)
+    return fail(PA_ERR_INVALID_ARGUMENT, "null pointer passed to paged_attention");
+  if (partitioned && (!exp_sums || !max_logits || !tmp_out))
+    return fail(PA_ERR_WORKSPACE, "paged_attention_v2 needs exp_sums, max_logits and tmp_out");
+  if (num_seqs < 0 || max_context_len < 0 || max_num_blocks_per_seq < 0)
+    return fail(PA_ERR_INVALID_ARGUMENT, "negative size passed to paged_attention");
+  AttnArgs a;
+  a.out = out;
+  a.exp_sums = exp_sums;
+  a.max_logits = max_logits;
+  a.tmp_out = tmp_out;
+  a.query = query;
+  a.key_cache = key_cache;
+  a.value_cache = value_cache;
+  a.block_tables = block_tables;
+  a.context_lens = context_lens;
+  a.alibi_slopes = alibi_slopes;
+  a.num_kv_heads = num_kv_heads;
+  a.num_seqs = num_seqs;
+  a.num_heads = num_heads;
+  a.head_size = head_size;
+  a.block_size = block_size;
+  a.max_context_len = max_context_len;
+  a.max_num_blocks_per_seq = max_num_blocks_per_seq;
+  a.q_stride = q_stride;
+  a.kv_block_stride = kv_block_stride;
+  a.kv_head_stride = kv_head_stride;
+  a.dtype = dtype;
+  a.kv_dtype = kv_cache_dtype;
+  a.scale = scale;
+  a.softcap = softcapping;
+  a.k_scale = kv_cache_dtype == DT_FP8 ? k_scale : 1.f;
+  a.v_scale = kv_cache_dtype == DT_FP8 ? v_scale : 1.f;
+  a.partitioned = partitioned;
+  return launch_paged_attention(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int paged_attention_v1_ex(void* out, const void* query, const void* key_cache, const void* value_cache,
+                          int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                          const uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                          int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                          int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                          const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
+                          int64_t stream) {
+  return attention_entry(false, out, nullptr, nullptr, nullptr, query, key_cache, value_cache, num_kv_heads, scale,
+                         block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
+                         max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
+                         alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
+}
+
+int paged_attention_v2_ex(void* out, float* exp_sums, float* max_logits, void* tmp_out, const void* query,
+                          const void* key_cache, const void* value_cache, int32_t num_kv_heads, float scale,
+                          const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
+                          int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                          int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
+                          int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
+                          uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream) {
+  return attention_entry(true, out, exp_sums, max_logits, tmp_out, query, key_cache, value_cache, num_kv_heads, scale,
+                         block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
+                         max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
+                         alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
+}
+
+void paged_attention_v1(void* out, void* query, void* key_cache, void* value_cache, int32_t num_kv_heads, float scale,
+                        uint32_t* block_tables, uint32_t* context_lens, int32_t block_size, int32_t max_context_len,
+                        int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq,
+                        int32_t q_stride, int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype,
+                        float softscapping, int64_t stream) {
+  (void)paged_attention_v1_ex(out, query, key_cache, value_cache, num_kv_heads, scale, block_tables, context_lens,
+                              block_size, max_context_len, num_seqs, num_heads, head_size, max_num_blocks_per_seq,
+                              q_stride, kv_block_stride, kv_head_stride, dtype, softscapping, nullptr, dtype, 1.f, 1.f,
+                              stream);
+}
+
+void paged_attention_v2(void* out, float* exp_sums, float* max_logits, void* tmp_out, void* query, void* key_cache,
+                        void* value_cache, int32_t num_kv_heads, float scale, uint32_t* block_tables,
+                        uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                        int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                        int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                        int64_t stream) {
+  (void)paged_attention_v2_ex(out, exp_sums, max_logits, tmp_out, query, key_cache, value_cache, num_kv_heads, scale,
+                              block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
+                              max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
+                              nullptr, dtype, 1.f, 1.f, stream);
+}
+
+const char* pa_last_error(void) { return t_error; }
+
+unsigned pa_device_status(int clear) {
+  unsigned v = 0u;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 0xffffffffu;
+  if (cudaMemcpyFromSymbol(&v, g_status_word, sizeof(v)) != cudaSuccess) return 0xffffffffu;
+  if (clear && v != 0u) {
+    const unsigned zero = 0u;
+    cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero));
+  }
+  return v;
+}
+
+const char* pa_version(void) { return "0.1.0"; }
+
+}  // extern "C"

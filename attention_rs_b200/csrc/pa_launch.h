@@ -1,0 +1,61 @@
+// Host-side plumbing shared by the translation units of the library: argument
+// bundles, launcher prototypes, the per-thread error text.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pagedattention_b200.h"
+
+namespace pa {
+
+struct ReshapeArgs {
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;
+  int num_tokens, num_heads, head_size, block_size, x;
+  int64_t key_stride, value_stride;  // elements
+  uint32_t dtype, cache_dtype;
+  float k_scale, v_scale;
+};
+
+struct AttnArgs {
+  void* out;
+  float* exp_sums;    // null together with max_logits / tmp_out: single pass
+  float* max_logits;
+  void* tmp_out;
+  const void* query;
+  const void* key_cache;
+  const void* value_cache;
+  const uint32_t* block_tables;
+  const uint32_t* context_lens;
+  const float* alibi_slopes;
+  int num_kv_heads, num_seqs, num_heads, head_size, block_size;
+  int max_context_len, max_num_blocks_per_seq, q_stride;
+  int64_t kv_block_stride, kv_head_stride;  // elements
+  uint32_t dtype, kv_dtype;
+  float scale, softcap, k_scale, v_scale;
+  bool partitioned;
+};
+
+// Each returns a PA_* status and never synchronises.
+int launch_reshape_and_cache(const ReshapeArgs& a, cudaStream_t stream);
+int launch_paged_attention(const AttnArgs& a, cudaStream_t stream);
+
+// Tensor-core kernel family, one translation unit per (query dtype, cache kind).
+// Returns PA_ERR_UNSUPPORTED when (head_size, block_size) is not compiled in.
+struct DecodeParams;
+int launch_decode_mma_f16(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream);
+int launch_decode_mma_bf16(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream);
+int launch_decode_mma_f16_fp8(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream);
+int launch_decode_mma_bf16_fp8(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream);
+
+// Device address of the status word of the current device (set up on first use).
+unsigned* device_status_word();
+
+// Records msg as the calling thread's last error and returns code.
+int fail(int code, const char* fmt, ...);
+
+}  // namespace pa

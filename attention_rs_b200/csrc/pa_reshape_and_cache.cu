@@ -1,0 +1,223 @@
+// reshape_and_cache for sm_100a: scatter of new key / value rows into the paged
+// caches, optionally quantising to FP8 E4M3 on the way.
+//
+// Semantics are those of src/kernels/src/reshape_and_cache_kernel.cu:14-59 of the
+// reference: token i goes to slot slot_mapping[i] (block = slot / block_size,
+// offset = slot % block_size); negative slots are padding and are skipped;
+//   key_cache  [num_blocks, num_heads, head_size/x, block_size, x]
+//   value_cache[num_blocks, num_heads, head_size, block_size].
+//
+// The reference moves one element per thread with 2-byte loads and stores.  Here a
+// CTA takes 32 consecutive tokens:
+//  * keys move as whole 16-byte chunks (x elements), one load and one store each;
+//  * for values the CTA first groups its tokens by destination block.  Along a
+//    value-cache row the tokens of one block are adjacent, so wherever a group
+//    fills an aligned 16-byte piece of a row (the normal case for a prefill whose
+//    slots run consecutively) the piece is gathered in registers and written with
+//    one 16-byte store; isolated tokens fall back to single-element stores.
+// A scalar kernel covers shapes the fast path does not take (block sizes other
+// than 8 / 16 / 32, x * sizeof(element) != 16, misaligned views).
+#include "pa_common.cuh"
+#include "pa_launch.h"
+
+namespace pa {
+namespace {
+
+constexpr int RC_TOKENS = 32;   // tokens per CTA (one warp builds the grouping)
+constexpr int RC_THREADS = 256;
+
+template <typename S, typename D, bool QUANT>
+__device__ __forceinline__ D convert_elem(S v, float scale) {
+  if constexpr (!QUANT) {
+    return v;  // S == D: raw bits
+  } else {
+    return f32_to_e4m3(__fdiv_rn(to_f32<S>(v), scale));
+  }
+}
+
+template <typename D, int N>
+struct alignas(sizeof(D) * N) Pack {
+  D v[N];
+};
+
+// S: source element (raw uint16_t / uint32_t when copying; __half / __nv_bfloat16 / float when quantising)
+// D: cache element (same raw type, or uint8_t for FP8)
+template <typename S, typename D, bool QUANT, int BS>
+__global__ void __launch_bounds__(RC_THREADS)
+reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value, D* __restrict__ key_cache,
+                         D* __restrict__ value_cache, const int64_t* __restrict__ slot_mapping, int num_tokens,
+                         int num_heads, int head_size, int64_t key_stride, int64_t value_stride, float k_scale,
+                         float v_scale) {
+  constexpr int X = 16 / sizeof(D);                 // cache elements per 16-byte key chunk
+  constexpr int PIECE = X < BS ? X : BS;            // elements of a value row written by one wide store
+  constexpr int NPIECE = BS / PIECE;
+  __shared__ int64_t s_blk[RC_TOKENS];              // destination block of token j (-1: padding)
+  __shared__ int s_off[RC_TOKENS];
+  __shared__ int64_t g_blk[RC_TOKENS];              // destination block of group g
+  __shared__ unsigned g_mask[RC_TOKENS];            // offsets present in group g
+  __shared__ signed char g_map[RC_TOKENS][BS];      // offset -> token index within the CTA
+  __shared__ int s_ngroups;
+
+  const int tok0 = blockIdx.x * RC_TOKENS;
+  const int ntok = min(RC_TOKENS, num_tokens - tok0);
+  const int tid = threadIdx.x;
+  const int n = num_heads * head_size;
+
+  if (tid < RC_TOKENS) {
+    const int lane = tid;
+    int64_t blk = -1;
+    int off = 0;
+    if (lane < ntok) {
+      const int64_t slot = slot_mapping[tok0 + lane];
+      if (slot >= 0) { blk = slot / BS; off = static_cast<int>(slot % BS); }
+    }
+    s_blk[lane] = blk;
+    s_off[lane] = off;
+    g_mask[lane] = 0u;
+    // Leader of a block = first lane that targets it.
+    int leader = lane;
+    for (int i = 0; i < RC_TOKENS; ++i) {
+      const int64_t other = __shfl_sync(0xffffffffu, blk, i);
+      if (other == blk && i < leader) leader = i;
+    }
+    const unsigned leaders = __ballot_sync(0xffffffffu, blk >= 0 && leader == lane);
+    if (lane == 0) s_ngroups = __popc(leaders);
+    __syncwarp();
+    if (blk >= 0) {
+      const int g = __popc(leaders & ((1u << leader) - 1u));
+      if (leader == lane) g_blk[g] = blk;
+      atomicOr(&g_mask[g], 1u << off);
+      g_map[g][off] = static_cast<signed char>(lane);
+    }
+  }
+  __syncthreads();
+
+  // ---- keys: one 16-byte chunk of the cache per thread-iteration
+  const int chunks_per_tok = n / X;
+  const int cph = head_size / X;  // chunks per head
+  for (int j = 0; j < ntok; ++j) {
+    const int64_t blk = s_blk[j];
+    if (blk < 0) continue;
+    const int off = s_off[j];
+    const S* src = key + (tok0 + j) * key_stride;
+    for (int c = tid; c < chunks_per_tok; c += RC_THREADS) {
+      const int h = c / cph, ci = c % cph;
+      Pack<D, X> outv;
+      if constexpr (!QUANT) {
+        outv = *reinterpret_cast<const Pack<D, X>*>(src + c * X);
+      } else {
+        const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src + c * X);
+#pragma unroll
+        for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
+      }
+      D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + off) * X;
+      *reinterpret_cast<Pack<D, X>*>(dst) = outv;
+    }
+  }
+
+  // ---- values: rows of the cache, grouped by destination block
+  const int ngroups = s_ngroups;
+  for (int row = tid; row < n; row += RC_THREADS) {
+    const S* src = value + tok0 * value_stride + row;
+    for (int g = 0; g < ngroups; ++g) {
+      const unsigned mask = g_mask[g];
+      D* dst = value_cache + (g_blk[g] * n + row) * BS;
+      if ((mask & (mask - 1u)) == 0u) {  // a single token in this block
+        const int off = __ffs(mask) - 1;
+        dst[off] = convert_elem<S, D, QUANT>(src[g_map[g][off] * value_stride], v_scale);
+        continue;
+      }
+#pragma unroll
+      for (int pc = 0; pc < NPIECE; ++pc) {
+        constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
+        const unsigned sub = (mask >> (pc * PIECE)) & FULL;
+        if (sub == 0u) continue;
+        if (sub == FULL) {
+          Pack<D, PIECE> outv;
+#pragma unroll
+          for (int e = 0; e < PIECE; ++e)
+            outv.v[e] = convert_elem<S, D, QUANT>(src[g_map[g][pc * PIECE + e] * value_stride], v_scale);
+          *reinterpret_cast<Pack<D, PIECE>*>(dst + pc * PIECE) = outv;
+        } else {
+#pragma unroll
+          for (int e = 0; e < PIECE; ++e)
+            if (sub & (1u << e))
+              dst[pc * PIECE + e] = convert_elem<S, D, QUANT>(src[g_map[g][pc * PIECE + e] * value_stride], v_scale);
+        }
+      }
+    }
+  }
+}
+
+// Element-per-thread fallback, any block size / x / alignment.
+template <typename S, typename D, bool QUANT>
+__global__ void reshape_and_cache_scalar_kernel(const S* __restrict__ key, const S* __restrict__ value,
+                                                D* __restrict__ key_cache, D* __restrict__ value_cache,
+                                                const int64_t* __restrict__ slot_mapping, int num_heads, int head_size,
+                                                int block_size, int x, int64_t key_stride, int64_t value_stride,
+                                                float k_scale, float v_scale) {
+  const int64_t tok = blockIdx.x;
+  const int64_t slot = slot_mapping[tok];
+  if (slot < 0) return;
+  const int64_t blk = slot / block_size, off = slot % block_size;
+  const int n = num_heads * head_size;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / head_size, d = i % head_size;
+    const int64_t kdst = (((blk * num_heads + h) * (head_size / x) + d / x) * block_size + off) * x + d % x;
+    const int64_t vdst = ((blk * num_heads + h) * static_cast<int64_t>(head_size) + d) * block_size + off;
+    key_cache[kdst] = convert_elem<S, D, QUANT>(key[tok * key_stride + i], k_scale);
+    value_cache[vdst] = convert_elem<S, D, QUANT>(value[tok * value_stride + i], v_scale);
+  }
+}
+
+template <typename S, typename D, bool QUANT>
+int launch_typed(const ReshapeArgs& a, cudaStream_t stream) {
+  const S* key = reinterpret_cast<const S*>(a.key);
+  const S* value = reinterpret_cast<const S*>(a.value);
+  D* kc = reinterpret_cast<D*>(a.key_cache);
+  D* vc = reinterpret_cast<D*>(a.value_cache);
+  constexpr int X = 16 / sizeof(D);
+  const bool aligned = (reinterpret_cast<uintptr_t>(a.key) % (X * sizeof(S)) == 0) &&
+                       ((a.key_stride * sizeof(S)) % (X * sizeof(S)) == 0) &&
+                       (reinterpret_cast<uintptr_t>(a.key_cache) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(a.value_cache) % 16 == 0);
+  const bool fast = aligned && a.x == X && a.head_size % X == 0 &&
+                    (a.block_size == 8 || a.block_size == 16 || a.block_size == 32);
+  if (a.num_tokens <= 0) return PA_OK;
+  if (fast) {
+    const int grid = (a.num_tokens + RC_TOKENS - 1) / RC_TOKENS;
+#define PA_RC_GO(BS)                                                                                               \
+  reshape_and_cache_kernel<S, D, QUANT, BS><<<grid, RC_THREADS, 0, stream>>>(                                      \
+      key, value, kc, vc, a.slot_mapping, a.num_tokens, a.num_heads, a.head_size, a.key_stride, a.value_stride,   \
+      a.k_scale, a.v_scale)
+    if (a.block_size == 8) PA_RC_GO(8);
+    else if (a.block_size == 16) PA_RC_GO(16);
+    else PA_RC_GO(32);
+#undef PA_RC_GO
+  } else {
+    const int threads = min(a.num_heads * a.head_size, 512);
+    reshape_and_cache_scalar_kernel<S, D, QUANT><<<a.num_tokens, threads, 0, stream>>>(
+        key, value, kc, vc, a.slot_mapping, a.num_heads, a.head_size, a.block_size, a.x, a.key_stride, a.value_stride,
+        a.k_scale, a.v_scale);
+  }
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+}  // namespace
+
+int launch_reshape_and_cache(const ReshapeArgs& a, cudaStream_t stream) {
+  if (a.cache_dtype == a.dtype) {
+    // Pure copy: move raw bits, so NaN payloads and negative zeros survive untouched.
+    if (a.dtype == DT_F16 || a.dtype == DT_BF16) return launch_typed<uint16_t, uint16_t, false>(a, stream);
+    if (a.dtype == DT_F32) return launch_typed<uint32_t, uint32_t, false>(a, stream);
+    return PA_ERR_UNSUPPORTED;
+  }
+  if (a.cache_dtype == DT_FP8) {
+    if (a.dtype == DT_F16) return launch_typed<__half, uint8_t, true>(a, stream);
+    if (a.dtype == DT_BF16) return launch_typed<__nv_bfloat16, uint8_t, true>(a, stream);
+    if (a.dtype == DT_F32) return launch_typed<float, uint8_t, true>(a, stream);
+  }
+  return PA_ERR_UNSUPPORTED;
+}
+
+}  // namespace pa

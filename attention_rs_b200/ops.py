@@ -1,0 +1,246 @@
+"""ctypes binding of libpagedattention_b200.so and the two public operators.
+
+Everything here is plumbing: tensors are described to the C ABI by pointer, shape
+and stride; validation, kernel choice and launches happen inside the library.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_LIB_NAME = "libpagedattention_b200.so"
+
+F16, BF16, F32, FP8_E4M3, U32, I64 = 0, 1, 2, 3, 16, 17
+PARTITION_SIZE = 512
+
+
+class PagedAttentionError(RuntimeError):
+    """Raised for every failure of the library (bad arguments, missing build, CUDA errors)."""
+
+
+class _Tensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_uint32), ("rank", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * 5), ("stride", ctypes.c_int64 * 5)]
+
+
+def library_path() -> str:
+    return os.path.join(_PKG_DIR, _LIB_NAME)
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads the CUDA library; raises if it has not been built (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        raise PagedAttentionError(
+            f"{path} is missing: build it with `python attention_rs_b200/csrc/build.py` "
+            "(needs nvcc; sm_100a only). This package has no CPU or PyTorch fallback.")
+    L = ctypes.CDLL(path)
+    vp, i32, u32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_int64, ctypes.c_float
+    tp = ctypes.POINTER(_Tensor)
+    L.call_reshape_and_cache.restype = None
+    L.call_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, u32, i64]
+    L.call_reshape_and_cache_ex.restype = ctypes.c_int
+    L.call_reshape_and_cache_ex.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, u32, u32, f32, f32, i64]
+    tail = [i32, f32, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, u32, f32]
+    L.paged_attention_v1.restype = None
+    L.paged_attention_v1.argtypes = [vp, vp, vp, vp] + tail + [i64]
+    L.paged_attention_v2.restype = None
+    L.paged_attention_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp] + tail + [i64]
+    L.paged_attention_v1_ex.restype = ctypes.c_int
+    L.paged_attention_v1_ex.argtypes = [vp, vp, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.paged_attention_v2_ex.restype = ctypes.c_int
+    L.paged_attention_v2_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.pa_paged_attention.restype = ctypes.c_int
+    L.pa_paged_attention.argtypes = [tp, tp, tp, tp, tp, tp, i64, f32, f32, f32, f32, tp, vp, ctypes.c_size_t, i64]
+    L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t
+    L.pa_paged_attention_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
+    L.pa_paged_attention_uses_partitions.restype = ctypes.c_int
+    L.pa_paged_attention_uses_partitions.argtypes = [i64, i64, i64, i64]
+    L.pa_reshape_and_cache.restype = ctypes.c_int
+    L.pa_reshape_and_cache.argtypes = [tp, tp, tp, tp, tp, f32, f32, i64]
+    L.pa_last_error.restype = ctypes.c_char_p
+    L.pa_device_status.restype = ctypes.c_uint
+    L.pa_device_status.argtypes = [ctypes.c_int]
+    L.pa_version.restype = ctypes.c_char_p
+    _lib = L
+    return L
+
+
+_FLOAT_CODES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype in _FLOAT_CODES:
+        return _FLOAT_CODES[t.dtype]
+    if t.dtype in (torch.uint8, getattr(torch, "float8_e4m3fn", torch.uint8)):
+        return FP8_E4M3
+    if t.dtype in (torch.int32, getattr(torch, "uint32", torch.int32)):
+        return U32
+    if t.dtype == torch.int64:
+        return I64
+    raise PagedAttentionError(f"dtype {t.dtype} is not supported")
+
+
+def _desc(t: Optional[torch.Tensor]) -> Optional[_Tensor]:
+    if t is None:
+        return None
+    if t.dim() > 5:
+        raise PagedAttentionError(f"tensor of rank {t.dim()} is not supported")
+    d = _Tensor()
+    d.data = t.data_ptr()
+    d.dtype = dtype_code(t)
+    d.rank = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise PagedAttentionError("all tensors must be CUDA tensors: this library has no CPU path "
+                                      "(the reference's operators bail on CPU as well)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise PagedAttentionError("all tensors must live on the same device")
+    if dev is None:
+        raise PagedAttentionError("no tensor given")
+    return dev
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise PagedAttentionError(load_library().pa_last_error().decode() or f"error code {rc}")
+
+
+def _ref(d: Optional[_Tensor]):
+    return None if d is None else ctypes.byref(d)
+
+
+def workspace_bytes(num_seqs: int, num_heads: int, head_size: int, max_context_len: int, dtype: torch.dtype) -> int:
+    return int(load_library().pa_paged_attention_workspace_bytes(num_seqs, num_heads, head_size, max_context_len,
+                                                                 _FLOAT_CODES[dtype]))
+
+
+def uses_partitions(num_seqs: int, num_heads: int, num_kv_heads: int, max_context_len: int) -> bool:
+    return bool(load_library().pa_paged_attention_uses_partitions(num_seqs, num_heads, num_kv_heads, max_context_len))
+
+
+def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_tables: torch.Tensor,
+                    context_lens: torch.Tensor, alibi_slopes: Optional[torch.Tensor], max_context_len: int,
+                    softmax_scale: float, softcapping: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0,
+                    out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention over a paged KV cache; mirror of the reference's ``paged_attention``
+    (src/paged_attention.rs:515-537).
+
+    q [num_seqs, num_heads, head_size] (f16 / bf16 / f32); key_cache
+    [num_blocks, num_kv_heads, head_size/x, block_size, x]; value_cache
+    [num_blocks, num_kv_heads, head_size, block_size]; block_tables int32/uint32
+    [num_seqs, max_blocks]; context_lens int32/uint32 [num_seqs]; alibi_slopes f32
+    [num_heads] or None.  ``softcapping == 1.0`` disables the soft-cap.  A uint8 /
+    float8_e4m3fn cache selects the FP8 mode, where ``k_scale`` / ``v_scale`` apply.
+    Returns a new tensor shaped like q (or fills ``out``).
+    """
+    L = load_library()
+    dev = _require_cuda(q, key_cache, value_cache, block_tables, context_lens, alibi_slopes, out, workspace)
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        ws_ptr, ws_len = None, 0
+        if q.dim() == 3 and q.dtype in _FLOAT_CODES and key_cache.dim() == 5:
+            ns, nh, hs = q.shape
+            if uses_partitions(ns, nh, key_cache.shape[1], max_context_len):
+                need = workspace_bytes(ns, nh, hs, max_context_len, q.dtype)
+                if workspace is None or workspace.numel() * workspace.element_size() < need:
+                    workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+                ws_ptr, ws_len = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = L.pa_paged_attention(_ref(_desc(q)), _ref(_desc(key_cache)), _ref(_desc(value_cache)),
+                                  _ref(_desc(block_tables)), _ref(_desc(context_lens)), _ref(_desc(alibi_slopes)),
+                                  int(max_context_len), float(softmax_scale), float(softcapping), float(k_scale),
+                                  float(v_scale), _ref(_desc(out)), ws_ptr, ws_len, stream)
+    _check(rc)
+    return out
+
+
+def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                      slot_mapping: torch.Tensor, k_scale: float = 1.0, v_scale: float = 1.0) -> None:
+    """Scatters new key / value rows into the paged caches in place; mirror of the
+    reference's ``reshape_and_cache`` (src/paged_attention.rs:890-904).
+
+    key, value [num_tokens, num_heads, head_size]; slot_mapping int64 [num_tokens],
+    negative entries are padding.  A uint8 / float8_e4m3fn cache is filled with
+    ``sat_e4m3(x / scale)``.
+    """
+    L = load_library()
+    dev = _require_cuda(key, value, key_cache, value_cache, slot_mapping)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = L.pa_reshape_and_cache(_ref(_desc(key)), _ref(_desc(value)), _ref(_desc(key_cache)), _ref(_desc(value_cache)),
+                                    _ref(_desc(slot_mapping)), float(k_scale), float(v_scale), stream)
+    _check(rc)
+
+
+# ---------------------------------------------------------------- raw C-ABI calls (drop-in symbols)
+
+def _attn_tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping):
+    ns, nh, hs = q.shape
+    return [key_cache.shape[1], float(scale), block_tables.data_ptr(), context_lens.data_ptr(), key_cache.shape[3],
+            int(max_context_len), ns, nh, hs, block_tables.shape[1], q.stride(0), key_cache.stride(0),
+            key_cache.stride(1), dtype_code(q), float(softcapping)]
+
+
+def paged_attention_v1(out, q, key_cache, value_cache, block_tables, context_lens, max_context_len, scale,
+                       softcapping=1.0, alibi_slopes=None, k_scale=1.0, v_scale=1.0, legacy=False) -> None:
+    """Direct call of the single-pass entry point (``paged_attention_v1`` when ``legacy``,
+    else ``paged_attention_v1_ex``)."""
+    L = load_library()
+    dev = _require_cuda(out, q, key_cache, value_cache, block_tables, context_lens, alibi_slopes)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        head = [out.data_ptr(), q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr()]
+        tail = _attn_tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping)
+        if legacy:
+            L.paged_attention_v1(*head, *tail, stream)
+        else:
+            _check(L.paged_attention_v1_ex(*head, *tail, None if alibi_slopes is None else alibi_slopes.data_ptr(),
+                                           dtype_code(key_cache), float(k_scale), float(v_scale), stream))
+
+
+def paged_attention_v2(out, exp_sums, max_logits, tmp_out, q, key_cache, value_cache, block_tables, context_lens,
+                       max_context_len, scale, softcapping=1.0, alibi_slopes=None, k_scale=1.0, v_scale=1.0,
+                       legacy=False) -> None:
+    """Direct call of the partitioned entry point (``paged_attention_v2`` / ``_ex``)."""
+    L = load_library()
+    dev = _require_cuda(out, exp_sums, max_logits, tmp_out, q, key_cache, value_cache, block_tables, context_lens,
+                        alibi_slopes)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        head = [out.data_ptr(), exp_sums.data_ptr(), max_logits.data_ptr(), tmp_out.data_ptr(), q.data_ptr(),
+                key_cache.data_ptr(), value_cache.data_ptr()]
+        tail = _attn_tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping)
+        if legacy:
+            L.paged_attention_v2(*head, *tail, stream)
+        else:
+            _check(L.paged_attention_v2_ex(*head, *tail, None if alibi_slopes is None else alibi_slopes.data_ptr(),
+                                           dtype_code(key_cache), float(k_scale), float(v_scale), stream))
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the current device (0 = healthy); synchronises."""
+    return int(load_library().pa_device_status(1 if clear else 0))

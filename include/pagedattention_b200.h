@@ -1,0 +1,194 @@
+/*
+ * C ABI of the sm_100a paged-attention library (libpagedattention_b200.so).
+ *
+ * Three groups of entry points:
+ *
+ *  1. The reference's own FFI, symbol for symbol, so the library links in place of
+ *     the reference's kernel archive: call_reshape_and_cache, paged_attention_v1,
+ *     paged_attention_v2.  They return void and report nothing, exactly like the
+ *     functions they replace.
+ *  2. "_ex" variants of the same three calls that add what the reference's C ABI
+ *     cannot carry (ALiBi slopes, an FP8-E4M3 cache, per-tensor scales) and return
+ *     a status code.
+ *  3. A host-side mirror of the reference's Rust operators paged_attention() and
+ *     reshape_and_cache(): tensor descriptors in, full shape / dtype validation
+ *     with the reference's error messages, v1 / v2 selection, then the kernels.
+ *
+ * Every pointer to tensor data is a DEVICE pointer owned by the caller.  Unless a
+ * function's comment says otherwise the library allocates nothing, frees nothing,
+ * never synchronises and never changes the current device; launches are
+ * asynchronous on the given stream (a CUstream / cudaStream_t cast to int64).
+ * Strides are in elements.
+ *
+ * File:line citations are relative to the reference project root.
+ */
+#ifndef PAGEDATTENTION_B200_H_
+#define PAGEDATTENTION_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element type codes.  0..2 are the reference's (src/kernels/src/pagedattention.cu:723,
+ * src/paged_attention.rs:34-39); the others are additions of this library. */
+#define PA_DTYPE_F16 0u
+#define PA_DTYPE_BF16 1u
+#define PA_DTYPE_F32 2u
+#define PA_DTYPE_FP8_E4M3 3u /* KV-cache storage only */
+#define PA_DTYPE_U32 16u     /* block_tables, context_lens */
+#define PA_DTYPE_I64 17u     /* slot_mapping */
+
+/* Status codes of the int-returning entry points. */
+#define PA_OK 0
+#define PA_ERR_INVALID_ARGUMENT 1 /* bad shape / dtype / stride / null pointer; nothing was launched */
+#define PA_ERR_UNSUPPORTED 2      /* combination not compiled in; nothing was launched */
+#define PA_ERR_CUDA 3             /* the CUDA runtime reported an error at launch */
+#define PA_ERR_WORKSPACE 4        /* workspace missing or too small */
+
+/* Context partition of the v2 path, in tokens.  Fixed by the reference's host code
+ * (src/paged_attention.rs:158, src/kernels/src/pagedattention.cu:768), which sizes
+ * tmp_out / exp_sums / max_logits for it. */
+#define PA_PARTITION_SIZE 512
+
+/* ------------------------------------------------------------------------------------------
+ * 1. Drop-in symbols
+ * ---------------------------------------------------------------------------------------- */
+
+/* Replaces call_reshape_and_cache, src/kernels/src/reshape_and_cache_kernel.cu:78-107
+ * (Rust prototype src/kernels/src/ffi.rs:4-20).
+ * key, value: [num_tokens, num_heads, head_size], row strides key_stride / value_stride.
+ * key_cache: [num_blocks, num_heads, head_size/x, block_size, x], value_cache:
+ * [num_blocks, num_heads, head_size, block_size], both contiguous.
+ * slot_mapping[i] < 0 marks a padding token, which is skipped. */
+void call_reshape_and_cache(void* key, void* value, void* key_cache, void* value_cache, int64_t* slot_mapping,
+                            int32_t num_tokens, int32_t num_heads, int32_t head_size, int32_t block_size, int32_t x,
+                            int32_t key_stride, int32_t value_stride, uint32_t dtype, int64_t stream);
+
+/* Replaces paged_attention_v1, src/kernels/src/pagedattention.cu:703-734
+ * (Rust prototype src/kernels/src/ffi.rs:22-45).  Single pass; no workspace.
+ * out, query: [num_seqs, num_heads, head_size]; block_tables: u32 [num_seqs,
+ * max_num_blocks_per_seq]; context_lens: u32 [num_seqs].
+ * softscapping == 1.0 disables the tanh soft-cap. */
+void paged_attention_v1(void* out, void* query, void* key_cache, void* value_cache, int32_t num_kv_heads, float scale,
+                        uint32_t* block_tables, uint32_t* context_lens, int32_t block_size, int32_t max_context_len,
+                        int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq,
+                        int32_t q_stride, int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype,
+                        float softscapping, int64_t stream);
+
+/* Replaces paged_attention_v2, src/kernels/src/pagedattention.cu:885-919
+ * (Rust prototype src/kernels/src/ffi.rs:47-73).  Context split into partitions of
+ * PA_PARTITION_SIZE tokens plus a log-sum-exp merge.  The caller provides the
+ * scratch buffers, sized for P = ceil(max_context_len / PA_PARTITION_SIZE):
+ * tmp_out [num_seqs, num_heads, P, head_size] of the query dtype, exp_sums and
+ * max_logits f32 [num_seqs, num_heads, P].  Their contents on return are private
+ * to the library. */
+void paged_attention_v2(void* out, float* exp_sums, float* max_logits, void* tmp_out, void* query, void* key_cache,
+                        void* value_cache, int32_t num_kv_heads, float scale, uint32_t* block_tables,
+                        uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                        int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                        int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                        int64_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * 2. Extended variants (status-returning)
+ * ---------------------------------------------------------------------------------------- */
+
+/* call_reshape_and_cache plus an optional FP8 cache: cache_dtype is either dtype
+ * (pure copy, bit-exact) or PA_DTYPE_FP8_E4M3, in which case every element is
+ * stored as sat_e4m3_rn(value / scale) with k_scale for keys and v_scale for values
+ * (IEEE fp32 division) and x counts cache elements (16 for FP8).
+ * Extends src/kernels/src/reshape_and_cache_kernel.cu:78-107. */
+int call_reshape_and_cache_ex(const void* key, const void* value, void* key_cache, void* value_cache,
+                              const int64_t* slot_mapping, int32_t num_tokens, int32_t num_heads, int32_t head_size,
+                              int32_t block_size, int32_t x, int32_t key_stride, int32_t value_stride, uint32_t dtype,
+                              uint32_t cache_dtype, float k_scale, float v_scale, int64_t stream);
+
+/* paged_attention_v1 plus: alibi_slopes (f32 [num_heads], may be NULL; the bias is
+ * slope * (token - context_len + 1), src/kernels/src/pagedattention.cu:235, which
+ * the reference's C ABI never passes, :621-622), kv_cache_dtype (dtype, or
+ * PA_DTYPE_FP8_E4M3 with element = e4m3 * scale), k_scale, v_scale.
+ * Extends src/kernels/src/pagedattention.cu:703-734. */
+int paged_attention_v1_ex(void* out, const void* query, const void* key_cache, const void* value_cache,
+                          int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                          const uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                          int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                          int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                          const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
+                          int64_t stream);
+
+/* paged_attention_v2 with the same additions.
+ * Extends src/kernels/src/pagedattention.cu:885-919. */
+int paged_attention_v2_ex(void* out, float* exp_sums, float* max_logits, void* tmp_out, const void* query,
+                          const void* key_cache, const void* value_cache, int32_t num_kv_heads, float scale,
+                          const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
+                          int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                          int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
+                          int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
+                          uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * 3. Host-side mirror of the reference's Rust operators
+ * ---------------------------------------------------------------------------------------- */
+
+/* A strided view of device memory: what the reference reads out of a candle
+ * Tensor's storage and Layout (src/paged_attention.rs:44-105). */
+typedef struct pa_tensor {
+  void* data;        /* device pointer of element [0,0,...] (start offset already applied) */
+  uint32_t dtype;    /* PA_DTYPE_* */
+  int32_t rank;      /* number of valid entries in shape / stride */
+  int64_t shape[5];
+  int64_t stride[5]; /* in elements */
+} pa_tensor;
+
+/* Mirror of paged_attention(), src/paged_attention.rs:515-537, and of the checks and
+ * dispatch of PagedAttention::cuda_fwd_t, src/paged_attention.rs:23-240.
+ *   q [num_seqs, num_heads, head_size]; key_cache rank 5; value_cache rank 4;
+ *   block_tables u32 [num_seqs, max_blocks]; context_lens u32 [num_seqs];
+ *   alibi_slopes f32 [num_heads] or NULL; out: like q, contiguous, caller-allocated.
+ * key_cache->dtype may be PA_DTYPE_FP8_E4M3 (then k_scale / v_scale apply).
+ * workspace: device scratch of at least pa_paged_attention_workspace_bytes(...) bytes,
+ * needed only when the partitioned path is chosen; pass NULL / 0 to force the
+ * single-pass path.  Returns PA_OK or an error code; pa_last_error() has the text. */
+int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_tensor* value_cache,
+                       const pa_tensor* block_tables, const pa_tensor* context_lens, const pa_tensor* alibi_slopes,
+                       int64_t max_context_len, float softmax_scale, float softcapping, float k_scale, float v_scale,
+                       const pa_tensor* out, void* workspace, size_t workspace_bytes, int64_t stream);
+
+/* Bytes of scratch the partitioned path wants for these sizes: tmp_out + exp_sums +
+ * max_logits as allocated at src/paged_attention.rs:199-203. */
+size_t pa_paged_attention_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t head_size,
+                                          int64_t max_context_len, uint32_t dtype);
+
+/* 1 if the dispatcher would take the partitioned (v2) path for these sizes when a
+ * workspace is available, else 0.  The reference's rule is at
+ * src/paged_attention.rs:158-161; this library uses its own (see DESIGN notes in
+ * the source). */
+int pa_paged_attention_uses_partitions(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
+                                       int64_t max_context_len);
+
+/* Mirror of reshape_and_cache(), src/paged_attention.rs:890-904, and of the checks of
+ * ReshapeCache::cuda_fwd_t, src/paged_attention.rs:547-689.
+ * key, value [num_tokens, num_heads, head_size]; slot_mapping i64 [num_tokens]. */
+int pa_reshape_and_cache(const pa_tensor* key, const pa_tensor* value, const pa_tensor* key_cache,
+                         const pa_tensor* value_cache, const pa_tensor* slot_mapping, float k_scale, float v_scale,
+                         int64_t stream);
+
+/* Text of the last error raised on the calling thread by an int-returning entry
+ * point ("" if none).  The pointer stays valid until the thread's next failing call. */
+const char* pa_last_error(void);
+
+/* Reads the status word kernels of this library write on the current device when a
+ * bounded wait gives up (0 = healthy); clears it if clear != 0.  Synchronises the
+ * device: for tests and diagnostics, not for the serving loop. */
+unsigned pa_device_status(int clear);
+
+/* Library version, "major.minor.patch". */
+const char* pa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAGEDATTENTION_B200_H_ */

@@ -1,0 +1,106 @@
+"""ctypes front-end of the reference's own CUDA kernels (test infrastructure).
+
+``oracle/_ref/libref_pa.so`` is the reference's pagedattention.cu and
+reshape_and_cache_kernel.cu compiled unchanged (recipe: ``make -C oracle ref``);
+``oracle/_ref/libref_alibi.so`` is the harness that launches the reference's kernel
+templates with ALiBi slopes.  Both are git-ignored build products.  They are used to
+pin the CPU oracle, as the second opinion in the GPU parity tests, and by the
+benchmark's reference leg; never by the product path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_PA = os.path.join(HERE, "_ref", "libref_pa.so")
+REF_ALIBI = os.path.join(HERE, "_ref", "libref_alibi.so")
+
+_DT = None
+
+
+def _codes():
+    global _DT
+    if _DT is None:
+        import torch
+        _DT = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+    return _DT
+
+
+def available() -> bool:
+    return os.path.exists(REF_PA)
+
+
+def alibi_available() -> bool:
+    return os.path.exists(REF_ALIBI)
+
+
+_libs = {}
+
+
+def _lib(path):
+    if path not in _libs:
+        L = ctypes.CDLL(path)
+        vp, i32, u32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_int64, ctypes.c_float
+        tail = [i32, f32, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, u32, f32]
+        if path == REF_PA:
+            L.call_reshape_and_cache.restype = None
+            L.call_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, u32, i64]
+            L.paged_attention_v1.restype = None
+            L.paged_attention_v1.argtypes = [vp, vp, vp, vp] + tail + [i64]
+            L.paged_attention_v2.restype = None
+            L.paged_attention_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp] + tail + [i64]
+        else:
+            L.ref_paged_attention_v2_alibi.restype = ctypes.c_int
+            L.ref_paged_attention_v2_alibi.argtypes = [vp, vp, vp, vp, vp, vp, vp] + tail + [vp, i64]
+        _libs[path] = L
+    return _libs[path]
+
+
+def _stream(t):
+    import torch
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping):
+    ns, nh, hs = q.shape
+    return [key_cache.shape[1], float(scale), block_tables.data_ptr(), context_lens.data_ptr(), key_cache.shape[3],
+            int(max_context_len), ns, nh, hs, block_tables.shape[1], q.stride(0), key_cache.stride(0),
+            key_cache.stride(1), _codes()[q.dtype], float(softcapping)]
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping):
+    nt, nh, hs = key.shape
+    _lib(REF_PA).call_reshape_and_cache(key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                                        slot_mapping.data_ptr(), nt, nh, hs, key_cache.shape[3], key_cache.shape[4],
+                                        key.stride(0), value.stride(0), _codes()[key.dtype], _stream(key))
+
+
+def paged_attention_v1(out, q, key_cache, value_cache, block_tables, context_lens, max_context_len, scale,
+                       softcapping=1.0):
+    _lib(REF_PA).paged_attention_v1(out.data_ptr(), q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                                    *_tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping),
+                                    _stream(q))
+
+
+def v2_workspace(q, max_context_len):
+    import torch
+    ns, nh, hs = q.shape
+    parts = max((max_context_len + 511) // 512, 1)
+    return (torch.empty((ns, nh, parts), dtype=torch.float32, device=q.device),
+            torch.empty((ns, nh, parts), dtype=torch.float32, device=q.device),
+            torch.empty((ns, nh, parts, hs), dtype=q.dtype, device=q.device))
+
+
+def paged_attention_v2(out, q, key_cache, value_cache, block_tables, context_lens, max_context_len, scale,
+                       softcapping=1.0, workspace=None, alibi_slopes=None):
+    exp_sums, max_logits, tmp_out = workspace if workspace is not None else v2_workspace(q, max_context_len)
+    head = [out.data_ptr(), exp_sums.data_ptr(), max_logits.data_ptr(), tmp_out.data_ptr(), q.data_ptr(),
+            key_cache.data_ptr(), value_cache.data_ptr()]
+    tail = _tail(q, key_cache, block_tables, context_lens, scale, max_context_len, softcapping)
+    if alibi_slopes is None:
+        _lib(REF_PA).paged_attention_v2(*head, *tail, _stream(q))
+    else:
+        rc = _lib(REF_ALIBI).ref_paged_attention_v2_alibi(*head, *tail, alibi_slopes.data_ptr(), _stream(q))
+        if rc != 0:
+            raise RuntimeError(f"reference ALiBi harness: unsupported combination or launch error ({rc})")

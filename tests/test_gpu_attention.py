@@ -1,0 +1,216 @@
+"""GPU parity of the decode-attention kernels, called through the C ABI, against the CPU oracle
+and (where its build is present) the reference's own CUDA kernels."""
+import numpy as np
+import pytest
+
+from tests.helpers import case_to_device, from_torch_f32, make_case, tolerances
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import torch
+    return torch.device("cuda:0")
+
+
+def run_ours(c, d, mode, legacy=False):
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import ops
+    q = d["q"]
+    out = torch.full(q.shape, float("nan"), dtype=q.dtype, device=q.device)
+    mcl = c.max_context_len
+    if mode == "v1":
+        ops.paged_attention_v1(out, q, d["key_cache"], d["value_cache"], d["block_tables"], d["context_lens"], mcl,
+                               c.scale, c.softcapping, d["alibi_slopes"], c.k_scale, c.v_scale, legacy=legacy)
+    elif mode == "v2":
+        ns, nh, hs = q.shape
+        parts = max((mcl + 511) // 512, 1)
+        exp_sums = torch.full((ns, nh, parts), float("nan"), dtype=torch.float32, device=q.device)
+        max_logits = torch.full((ns, nh, parts), float("nan"), dtype=torch.float32, device=q.device)
+        tmp_out = torch.full((ns, nh, parts, hs), float("nan"), dtype=q.dtype, device=q.device)
+        ops.paged_attention_v2(out, exp_sums, max_logits, tmp_out, q, d["key_cache"], d["value_cache"],
+                               d["block_tables"], d["context_lens"], mcl, c.scale, c.softcapping, d["alibi_slopes"],
+                               c.k_scale, c.v_scale, legacy=legacy)
+    else:
+        out = pa.paged_attention(q, d["key_cache"], d["value_cache"], d["block_tables"], d["context_lens"],
+                                 d["alibi_slopes"], mcl, c.scale, c.softcapping, c.k_scale, c.v_scale)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return from_torch_f32(out)
+
+
+def check(got, want, dtype, kv_dtype=None, what=""):
+    max_tol, mean_tol = tolerances(dtype, kv_dtype)
+    assert not np.isnan(got).any(), f"NaN in output {what}"
+    err = np.abs(got - want)
+    assert err.max() <= max_tol, f"{what}: max-abs {err.max():.3e} > {max_tol}"
+    assert err.mean() <= mean_tol, f"{what}: mean-abs {err.mean():.3e} > {mean_tol}"
+
+
+CTX_EDGE = [1, 15, 16, 17, 31, 32, 33, 100, 511, 512, 513, 1025]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("mode", ["v1", "v2", "api"])
+def test_context_edges_gqa4_d128(dev, dtype, block_size, mode):
+    c = make_case(CTX_EDGE, 8, 2, 128, block_size, dtype, seed=3)
+    got = run_ours(c, case_to_device(c, dev), mode)
+    check(got, c.expected(), dtype, what=f"{dtype} bs{block_size} {mode}")
+
+
+@pytest.mark.parametrize("head_size", [64, 80, 96, 112, 128, 192, 256])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+def test_head_sizes(dev, head_size, block_size):
+    c = make_case([7, 130, 600], 4, 2, head_size, block_size, "bf16", seed=head_size + block_size)
+    d = case_to_device(c, dev)
+    want = c.expected()
+    for mode in ("v1", "v2"):
+        check(run_ours(c, d, mode), want, "bf16", what=f"d{head_size} bs{block_size} {mode}")
+
+
+@pytest.mark.parametrize("heads", [(4, 4), (8, 4), (8, 2), (8, 1), (16, 1), (12, 1), (40, 2), (34, 1)])
+def test_group_sizes(dev, heads):
+    nh, nkv = heads
+    c = make_case([3, 77, 530], nh, nkv, 128, 16, "f16", seed=nh * 7 + nkv)
+    d = case_to_device(c, dev)
+    want = c.expected()
+    for mode in ("v1", "v2"):
+        check(run_ours(c, d, mode), want, "f16", what=f"heads {heads} {mode}")
+
+
+def test_empty_context_and_zero_seqs(dev):
+    import torch
+    from attention_rs_b200 import ops
+    c = make_case([0, 5, 0, 700], 8, 2, 128, 16, "bf16", seed=11)
+    d = case_to_device(c, dev)
+    want = c.expected()
+    assert (want[0] == 0).all() and (want[2] == 0).all()
+    for mode in ("v1", "v2", "api"):
+        got = run_ours(c, d, mode)
+        check(got, want, "bf16", what=f"empty {mode}")
+        assert (got[0] == 0).all() and (got[2] == 0).all()
+    # zero sequences: a no-op that must not fail
+    q0 = d["q"][:0]
+    out0 = torch.empty_like(q0)
+    ops.paged_attention_v1(out0, q0, d["key_cache"], d["value_cache"], d["block_tables"][:0], d["context_lens"][:0], 0,
+                           c.scale)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode", ["v1", "v2"])
+@pytest.mark.parametrize("block_size", [16, 32])
+def test_softcap_and_alibi(dev, mode, block_size):
+    c = make_case([9, 250, 1300], 8, 2, 128, block_size, "bf16", seed=21, softcapping=30.0, alibi=True)
+    check(run_ours(c, case_to_device(c, dev), mode), c.expected(), "bf16", what=f"softcap+alibi {mode}")
+    c = make_case([9, 250, 1300], 8, 2, 128, block_size, "f16", seed=22, alibi=True)
+    check(run_ours(c, case_to_device(c, dev), mode), c.expected(), "f16", what=f"alibi {mode}")
+    c = make_case([9, 250, 1300], 8, 2, 128, block_size, "bf16", seed=23, softcapping=5.0, q_scale=4.0)
+    check(run_ours(c, case_to_device(c, dev), mode), c.expected(), "bf16", what=f"softcap {mode}")
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("head_size,block_size", [(128, 16), (128, 32), (64, 16), (256, 16), (96, 32), (192, 16)])
+@pytest.mark.parametrize("mode", ["v1", "v2"])
+def test_fp8_cache(dev, dtype, head_size, block_size, mode):
+    c = make_case([1, 19, 333, 1030], 16, 2, head_size, block_size, dtype, "fp8", seed=31 + head_size)
+    check(run_ours(c, case_to_device(c, dev), mode), c.expected(), dtype, "fp8", what=f"fp8 {dtype} d{head_size} {mode}")
+
+
+@pytest.mark.parametrize("combo", [("f32", None, 128, 16), ("f32", None, 80, 8), ("bf16", "fp8", 80, 16),
+                                   ("f16", "fp8", 128, 8), ("f32", "fp8", 64, 16)])
+@pytest.mark.parametrize("mode", ["v1", "v2"])
+def test_generic_kernel_combinations(dev, combo, mode):
+    dtype, kv, hs, bs = combo
+    c = make_case([2, 45, 520], 4, 2, hs, bs, dtype, kv, seed=41 + hs + bs)
+    check(run_ours(c, case_to_device(c, dev), mode), c.expected(), dtype, kv, what=f"generic {combo} {mode}")
+
+
+def test_legacy_symbols_match_ex(dev):
+    c = make_case([33, 700, 64], 8, 2, 128, 16, "bf16", seed=51)
+    d = case_to_device(c, dev)
+    for mode in ("v1", "v2"):
+        a = run_ours(c, d, mode, legacy=True)
+        b = run_ours(c, d, mode, legacy=False)
+        assert np.array_equal(a, b)
+        check(a, c.expected(), "bf16", what=f"legacy {mode}")
+
+
+def test_strided_query(dev):
+    """q split out of a fused qkv tensor: row stride larger than num_heads * head_size."""
+    import torch
+    import attention_rs_b200 as pa
+    c = make_case([50, 600], 8, 2, 128, 16, "bf16", seed=61)
+    d = case_to_device(c, dev)
+    ns, nh, hs = d["q"].shape
+    fused = torch.zeros((ns, nh + 4, hs), dtype=d["q"].dtype, device=dev)
+    fused[:, :nh] = d["q"]
+    qv = fused[:, :nh]
+    assert qv.stride(0) == (nh + 4) * hs
+    out = pa.paged_attention(qv, d["key_cache"], d["value_cache"], d["block_tables"], d["context_lens"], None,
+                             c.max_context_len, c.scale)
+    check(from_torch_f32(out), c.expected(), "bf16", what="strided q")
+
+
+def test_matches_reference_kernels(dev):
+    """Same inputs through the reference's own CUDA kernels (compiled unchanged): both must sit inside
+    the tolerance of the oracle, and so within twice the tolerance of each other."""
+    import torch
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("oracle/_ref not built")
+    for dtype in ("bf16", "f16"):
+        c = make_case([1, 16, 100, 513, 2000], 8, 2, 128, 16, dtype, seed=71, poison=False)
+        d = case_to_device(c, dev)
+        want = c.expected()
+        ref1 = torch.empty_like(d["q"])
+        ref_gpu.paged_attention_v1(ref1, d["q"], d["key_cache"], d["value_cache"], d["block_tables"], d["context_lens"],
+                                   c.max_context_len, c.scale)
+        ref2 = torch.empty_like(d["q"])
+        ref_gpu.paged_attention_v2(ref2, d["q"], d["key_cache"], d["value_cache"], d["block_tables"], d["context_lens"],
+                                   c.max_context_len, c.scale)
+        torch.cuda.synchronize()
+        check(from_torch_f32(ref1), want, dtype, what="reference v1 vs oracle")
+        check(from_torch_f32(ref2), want, dtype, what="reference v2 vs oracle")
+        for mode in ("v1", "v2"):
+            got = run_ours(c, d, mode)
+            check(got, want, dtype, what=f"ours {mode}")
+            assert np.abs(got - from_torch_f32(ref1)).max() <= 2 * tolerances(dtype)[0]
+
+
+def test_headline_shape_scaled(dev):
+    """Configuration 2's structure (GQA 32/8, d128, block 16, disjoint random tables) at 8 sequences."""
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import workloads
+    from oracle import oracle as O
+    w = workloads.decode_workload(2, num_seqs=8, ctx_range=(1024, 3000))
+    t = workloads.device_tensors(w, dev)
+    out = pa.paged_attention(t["q"], t["key_cache"], t["value_cache"], t["block_tables"], t["context_lens"], None,
+                             w.max_context_len, w.scale)
+    torch.cuda.synchronize()
+    kc = t["key_cache"].view(torch.int16).cpu().numpy().view(np.uint16)
+    vc = t["value_cache"].view(torch.int16).cpu().numpy().view(np.uint16)
+    q = t["q"].view(torch.int16).cpu().numpy().view(np.uint16)
+    want = O.paged_attention(q, kc, vc, w.block_tables, w.context_lens, w.scale, O.BF16)
+    check(from_torch_f32(out), want, "bf16", what="cfg2 scaled")
+
+
+def test_linearity_in_v_full_size_partition_count(dev):
+    """Size-independent property at a long context: attention is linear in V, so out(V1 + V2) must equal
+    out(V1) + out(V2) up to rounding, and a context shorter than one partition must not depend on the
+    partitioned / single-pass choice."""
+    import torch
+    from attention_rs_b200 import workloads
+    w = workloads.decode_workload(5, num_seqs=1, ctx_range=(40000, 40000))
+    t = workloads.device_tensors(w, dev)
+    import attention_rs_b200 as pa
+    args = (t["block_tables"], t["context_lens"], t["alibi_slopes"], w.max_context_len, w.scale)
+    v1 = t["value_cache"]
+    v2 = torch.randn(v1.shape, device=dev, dtype=torch.float32).to(v1.dtype)
+    o1 = pa.paged_attention(t["q"], t["key_cache"], v1, *args).float()
+    o2 = pa.paged_attention(t["q"], t["key_cache"], v2, *args).float()
+    o12 = pa.paged_attention(t["q"], t["key_cache"], (v1.float() + v2.float()).to(v1.dtype), *args).float()
+    assert (o12 - (o1 + o2)).abs().max().item() <= 2e-2

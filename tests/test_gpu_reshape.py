@@ -1,0 +1,182 @@
+"""GPU parity of reshape_and_cache through the C ABI: cache bytes must equal the oracle's (and the
+reference kernel's) bit for bit, for copies and for the FP8 quantising mode."""
+import zlib
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import DT, to_torch, torch_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import torch
+    return torch.device("cuda:0")
+
+
+def random_rows(rng, shape, dtype):
+    a = rng.standard_normal(shape, dtype=np.float32)
+    # sprinkle special values: they must be copied verbatim
+    flat = a.reshape(-1)
+    if flat.size >= 8:
+        flat[0], flat[1], flat[2], flat[3] = np.nan, np.inf, -np.inf, -0.0
+    return O.to_storage(a, dtype)
+
+
+def run_case(dev, num_tokens, num_heads, head_size, block_size, dtype, cache_dtype, slots, seed, stride_pad=0,
+             legacy=False, x=None):
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import ops
+    rng = np.random.default_rng(seed)
+    dt, cdt = DT[dtype], DT[cache_dtype]
+    nb = (int(slots.max()) // block_size + 2) if (slots >= 0).any() else 2
+    key = random_rows(rng, (num_tokens, num_heads + stride_pad, head_size), dt)
+    value = random_rows(rng, (num_tokens, num_heads + stride_pad, head_size), dt)
+    if cdt == O.FP8:
+        key = O.to_storage(np.nan_to_num(O.from_storage(key, dt), nan=0.5, posinf=3.0, neginf=-3.0), dt)
+        value = O.to_storage(np.nan_to_num(O.from_storage(value, dt), nan=0.5, posinf=3.0, neginf=-3.0), dt)
+    k_scale = v_scale = 1.0
+    if cdt == O.FP8:
+        k_scale, v_scale = 0.0123, 0.0217
+    kshape, vshape = O.cache_shapes(nb, num_heads, head_size, block_size, cdt)
+    if x is not None:
+        kshape = (nb, num_heads, head_size // x, block_size, x)
+    kc0 = rng.integers(0, 255, size=int(np.prod(kshape)) * O.ELEM_SIZE[cdt], dtype=np.uint8)
+    vc0 = rng.integers(0, 255, size=int(np.prod(vshape)) * O.ELEM_SIZE[cdt], dtype=np.uint8)
+    kc_want = kc0.copy().view(O.NP_STORAGE[cdt]).reshape(kshape)
+    vc_want = vc0.copy().view(O.NP_STORAGE[cdt]).reshape(vshape)
+    kview, vview = key[:, :num_heads], value[:, :num_heads]
+    O.reshape_and_cache(kview, vview, kc_want, vc_want, slots, dt, cdt, k_scale, v_scale)
+
+    tk, tv = to_torch(key, dt, dev)[:, :num_heads], to_torch(value, dt, dev)[:, :num_heads]
+    tkc = to_torch(kc0.copy().view(O.NP_STORAGE[cdt]).reshape(kshape), cdt, dev)
+    tvc = to_torch(vc0.copy().view(O.NP_STORAGE[cdt]).reshape(vshape), cdt, dev)
+    tslots = torch.from_numpy(slots).to(dev)
+    if legacy:
+        L = ops.load_library()
+        L.call_reshape_and_cache(tk.data_ptr(), tv.data_ptr(), tkc.data_ptr(), tvc.data_ptr(), tslots.data_ptr(),
+                                 num_tokens, num_heads, head_size, block_size, kshape[4], tk.stride(0), tv.stride(0),
+                                 dt, torch.cuda.current_stream().cuda_stream)
+    else:
+        pa.reshape_and_cache(tk, tv, tkc, tvc, tslots, k_scale, v_scale)
+    torch.cuda.synchronize()
+    assert np.array_equal(torch_bits(tkc).reshape(-1), kc_want.view(np.uint8).reshape(-1)), "key_cache bytes differ"
+    assert np.array_equal(torch_bits(tvc).reshape(-1), vc_want.view(np.uint8).reshape(-1)), "value_cache bytes differ"
+    return tk, tv, tslots, kc0, vc0, kshape, vshape, cdt
+
+
+def slot_patterns(rng, num_tokens, block_size, kind):
+    pool = max(4 * num_tokens, 64)
+    if kind == "contiguous":
+        return np.arange(num_tokens, dtype=np.int64) + 5
+    if kind == "aligned":
+        return np.arange(num_tokens, dtype=np.int64) + 2 * block_size
+    if kind == "random":
+        return rng.permutation(pool)[:num_tokens].astype(np.int64)
+    if kind == "padded":
+        s = rng.permutation(pool)[:num_tokens].astype(np.int64)
+        s[rng.random(num_tokens) < 0.3] = -1
+        return s
+    if kind == "runs":  # several sequences, each a contiguous run starting at an arbitrary slot
+        out, pos = [], 3
+        while len(out) < num_tokens:
+            n = int(rng.integers(1, 40))
+            out.extend(range(pos, pos + n))
+            pos += n + int(rng.integers(0, 50))
+        return np.array(out[:num_tokens], dtype=np.int64)
+    if kind == "all_padding":
+        return np.full(num_tokens, -1, dtype=np.int64)
+    raise ValueError(kind)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("kind", ["contiguous", "aligned", "random", "padded", "runs", "all_padding"])
+def test_copy_bit_exact(dev, dtype, block_size, kind):
+    rng = np.random.default_rng(zlib.crc32(repr((dtype, block_size, kind)).encode()))
+    slots = slot_patterns(rng, 77, block_size, kind)
+    run_case(dev, 77, 4, 64, block_size, dtype, dtype, slots, seed=1)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 64), (33, 8, 128), (5, 2, 256), (64, 3, 80), (200, 8, 128)])
+def test_copy_shapes_and_strides(dev, shape):
+    nt, nh, hs = shape
+    rng = np.random.default_rng(nt)
+    slots = slot_patterns(rng, nt, 16, "runs")
+    run_case(dev, nt, nh, hs, 16, "bf16", "bf16", slots, seed=2, stride_pad=0)
+    run_case(dev, nt, nh, hs, 16, "bf16", "bf16", slots, seed=3, stride_pad=2)     # rows of a fused qkv tensor
+    run_case(dev, nt, nh, hs, 16, "bf16", "bf16", slots, seed=4, legacy=True)      # the drop-in symbol
+
+
+def test_zero_tokens_and_odd_block_size(dev):
+    rng = np.random.default_rng(5)
+    run_case(dev, 0, 2, 64, 16, "bf16", "bf16", np.zeros(0, dtype=np.int64), seed=5)
+    run_case(dev, 19, 2, 64, 4, "bf16", "bf16", slot_patterns(rng, 19, 4, "random"), seed=6)   # scalar kernel
+    run_case(dev, 19, 2, 64, 16, "bf16", "bf16", slot_patterns(rng, 19, 16, "random"), seed=7, x=4)   # unusual x
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("kind", ["contiguous", "random", "padded"])
+def test_fp8_quantising_bit_exact(dev, dtype, block_size, kind):
+    rng = np.random.default_rng(zlib.crc32(repr((dtype, block_size, kind, 8)).encode()))
+    slots = slot_patterns(rng, 70, block_size, kind)
+    run_case(dev, 70, 4, 128, block_size, dtype, "fp8", slots, seed=8)
+
+
+def test_fp8_every_code_round_trips(dev):
+    """All 256 E4M3 codes written as bf16 values with scale 1 must come back as the same code
+    (NaN codes excepted), on the GPU kernel as in the oracle."""
+    import torch
+    import attention_rs_b200 as pa
+    codes = np.arange(256, dtype=np.uint8)
+    vals = O.from_storage(codes, O.FP8)
+    ok = ~np.isnan(vals)
+    rows = np.zeros((1, 1, 256), dtype=np.float32)
+    rows[0, 0, :] = np.where(ok, vals, 0.0)
+    key = to_torch(O.to_storage(rows, O.BF16), O.BF16, dev)
+    kc = torch.zeros((1, 1, 16, 16, 16), dtype=torch.uint8, device=dev)
+    vc = torch.zeros((1, 1, 256, 16), dtype=torch.uint8, device=dev)
+    pa.reshape_and_cache(key, key, kc, vc, torch.tensor([3], device=dev, dtype=torch.int64), 1.0, 1.0)
+    got = vc[0, 0, :, 3].cpu().numpy()
+    want = np.where(ok, codes, 0).astype(np.uint8)
+    want[want == 0x80] = 0x80  # -0 keeps its sign
+    assert np.array_equal(got[ok], want[ok])
+
+
+def test_matches_reference_kernel_config3(dev):
+    """Configuration 3 at full size (32768 tokens, 8 heads, d128, 65536 slots, ~2% padding): the cache bytes
+    must equal those written by the reference's own kernel, bit for bit."""
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import workloads
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("oracle/_ref not built")
+    for contiguous in (False, True):
+        w = workloads.scatter_workload(contiguous=contiguous)
+        g = torch.Generator(device=dev)
+        g.manual_seed(w.seed)
+        key = torch.randn((w.num_tokens, w.num_heads, w.head_size), generator=g, device=dev).to(torch.bfloat16)
+        value = torch.randn((w.num_tokens, w.num_heads, w.head_size), generator=g, device=dev).to(torch.bfloat16)
+        slots = torch.from_numpy(w.slot_mapping).to(dev)
+        kshape, vshape = workloads.cache_shapes(w.num_blocks, w.num_heads, w.head_size, w.block_size, "bf16")
+        init_k = torch.randn(kshape, generator=g, device=dev).to(torch.bfloat16)
+        init_v = torch.randn(vshape, generator=g, device=dev).to(torch.bfloat16)
+        kc_ref, vc_ref, kc, vc = init_k.clone(), init_v.clone(), init_k.clone(), init_v.clone()
+        ref_gpu.reshape_and_cache(key, value, kc_ref, vc_ref, slots)
+        pa.reshape_and_cache(key, value, kc, vc, slots)
+        torch.cuda.synchronize()
+        assert torch.equal(kc.view(torch.int16), kc_ref.view(torch.int16))
+        assert torch.equal(vc.view(torch.int16), vc_ref.view(torch.int16))
+        # property: every valid token can be read back from its slot, padding left the cache untouched
+        valid = slots >= 0
+        blk, off = slots[valid] // w.block_size, slots[valid] % w.block_size
+        back_v = vc[blk, :, :, off]
+        assert torch.equal(back_v.view(torch.int16), value[valid].view(torch.int16))
+        back_k = kc[blk, :, :, off, :].reshape(-1, w.num_heads, w.head_size)
+        assert torch.equal(back_k.view(torch.int16), key[valid].view(torch.int16))
