@@ -1,0 +1,417 @@
+"""Benchmark of the paged decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|4|5] [--gather]
+
+One step = one decode-attention pass (the partitioned entry point of the C ABI: main kernel plus
+partition merge) over one batch of the workload.  Metric: effective KV-cache read bandwidth in GB/s
+= algorithmic KV bytes of the step (sum of context lengths x kv heads x head size x 2 (K and V) x
+element size) / time, aggregated over ranks.  With N > 1 (launched by torchrun, one rank per GPU)
+the kv heads of an N-times-wider model are sharded over the ranks, each rank owning 8 kv heads and
+their cache slice: per-GPU work is fixed (weak scaling) and there is no collective on the attention
+path; --gather adds the optional all-gather of the outputs to the timed step.
+
+The line printed by rank 0 also carries: "e2e" (the same metric through the public Python operators
+with the step's inputs coming from pinned host memory and the result read back), "roofline" (HBM),
+"cpu_baseline" (the CPU restatement of the path timed on this box's host cores), "clocks".
+
+--impl reference times the CPU restatement of the reference's algorithm (the reference has no CPU
+path for these operators; see oracle/paged_oracle.c) and, as extra context, the reference's own CUDA
+kernels compiled unchanged when that build is present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "paged_decode_attention_effective_kv_bandwidth"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the main decode kernel for one launch of the
+# headline workload, from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: None}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the benchmark runs (read-only NVML)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+            return self
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def _run(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                util = int(nv.nvmlDeviceGetUtilizationRates(self._h).gpu)
+                bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                self.samples.append((mhz, util))
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        loaded = [m for m, u in self.samples if u > 0] or [m for m, _ in self.samples]
+        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def describe(w, n_gpus, gather):
+    return {
+        "workload": (f"{w.name}: paged decode attention, batch {w.num_seqs}, {w.num_heads} q / {w.num_kv_heads} kv heads "
+                     f"per GPU, head_dim {w.head_size}, block_size {w.block_size}, context U[{int(w.context_lens.min())},"
+                     f"{int(w.context_lens.max())}] (mean {float(w.context_lens.mean()):.0f}), q {w.dtype}, cache {w.kv_dtype}, "
+                     f"partitioned (v2) entry point, partition {512}"),
+        "kv_bytes_per_step_per_gpu": w.kv_bytes(),
+        "l2": "KV working set per GPU exceeds the 126 MB L2 many times over; no flush between steps",
+        "parallelism": f"kv-head sharding, {n_gpus} rank(s) x {w.num_kv_heads} kv heads, no collective on the attention path"
+                       + (" + all-gather of outputs" if gather else ""),
+        "seed": w.seed,
+    }
+
+
+# ---------------------------------------------------------------- our arm
+
+def run_ours(args):
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import ops, workloads
+
+    rank, world, local = dist_env()
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 --nproc-per-node N "
+                         "--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    pa.load_library()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = workloads.decode_workload(args.config, num_seqs=args.num_seqs)
+    w.seed = w.seed + 1000 * rank           # every rank owns different heads of the wider model
+    t = workloads.device_tensors(w, dev)
+    q, kc, vc, bt, cl = t["q"], t["key_cache"], t["value_cache"], t["block_tables"], t["context_lens"]
+    slopes, k_scale, v_scale = t["alibi_slopes"], t["k_scale"], t["v_scale"]
+    mcl = w.max_context_len
+    ns, nh, hs = q.shape
+    parts = (mcl + 511) // 512
+    out = torch.empty_like(q)
+    exp_sums = torch.empty((ns, nh, parts), dtype=torch.float32, device=dev)
+    max_logits = torch.empty_like(exp_sums)
+    tmp_out = torch.empty((ns, nh, parts, hs), dtype=q.dtype, device=dev)
+    gathered = torch.empty((world * ns, nh, hs), dtype=out.dtype, device=dev) if (args.gather and world > 1) else None
+
+    def step():
+        ops.paged_attention_v2(out, exp_sums, max_logits, tmp_out, q, kc, vc, bt, cl, mcl, w.scale, w.softcapping,
+                               slopes, k_scale, v_scale)
+        if gathered is not None:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    if ops.device_status() != 0:
+        raise SystemExit("a kernel reported a timed-out wait; the measurement is void")
+
+    # ---- end to end through the public operators: the step's inputs start in pinned host memory
+    new_k = torch.randn((ns, w.num_kv_heads, hs), device=dev).to(q.dtype)
+    h_q, h_k, h_v = q.cpu().pin_memory(), new_k.cpu().pin_memory(), new_k.flip(0).cpu().pin_memory()
+    last = (cl.long() - 1).clamp_(min=0)
+    slots = (bt.long().gather(1, (last // w.block_size).unsqueeze(1)).squeeze(1) * w.block_size + last % w.block_size)
+    h_slots, h_bt, h_cl = slots.cpu().pin_memory(), bt.cpu().pin_memory(), cl.cpu().pin_memory()
+    h_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    fp8 = w.kv_dtype == "fp8"
+
+    def e2e_step():
+        dq, dk, dv = h_q.to(dev, non_blocking=True), h_k.to(dev, non_blocking=True), h_v.to(dev, non_blocking=True)
+        ds, dbt, dcl = h_slots.to(dev, non_blocking=True), h_bt.to(dev, non_blocking=True), h_cl.to(dev, non_blocking=True)
+        pa.reshape_and_cache(dk, dv, kc, vc, ds, k_scale if fp8 else 1.0, v_scale if fp8 else 1.0)
+        o = pa.paged_attention(dq, kc, vc, dbt, dcl, slopes, mcl, w.scale, w.softcapping, k_scale, v_scale)
+        h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()    # the caller consumes the result before the next step
+
+    e2e_steps = max(10, min(args.steps, 200))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    h2d = sum(x.numel() * x.element_size() for x in (h_q, h_k, h_v, h_slots, h_bt, h_cl))
+    d2h = h_out.numel() * h_out.element_size()
+    clocks = sampler.stop() if sampler is not None else None
+
+    # ---- max over ranks
+    if dist is not None:
+        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(tt[0]), float(tt[1])
+        kvb = torch.tensor([w.kv_bytes()], device=dev, dtype=torch.float64)
+        dist.all_reduce(kvb, op=dist.ReduceOp.SUM)
+        total_kv = float(kvb[0])
+    else:
+        total_kv = float(w.kv_bytes())
+
+    if rank == 0:
+        per_step_ms = ms / args.steps
+        value = total_kv / (per_step_ms * 1e-3) / 1e9
+        e2e_value = total_kv / (e2e_ms / e2e_steps * 1e-3) / 1e9
+        peak, peak_kind = measured_peak()
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w.dtype if not fp8 else "fp8_e4m3 cache / bf16 query",
+            "data": "synthetic", "config": describe(w, world, args.gather),
+            "tokens_per_s": round(world * w.num_seqs / (per_step_ms * 1e-3), 1),
+            "pct_of_8TBps_nominal_per_gpu": round(100.0 * per_gpu / NOMINAL_HBM_GBS, 2),
+            "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 5),
+                    "path": "pinned host -> device copies, reshape_and_cache of the step's tokens, paged_attention, "
+                            "output copied back to pinned host memory"},
+            "gpu_launches": args.steps * 2,
+            "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(per_gpu / peak, 4), "peak_kind": f"of {peak_kind}",
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.config),
+                         "algorithmic_bytes_per_launch": w.kv_bytes(),
+                         "timed": "CUDA events around each step's launches (decode kernel + partition merge)"},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w, t, budget_s=args.cpu_budget)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------- CPU restatement (baseline / reference arm)
+
+class CpuPort:
+    """The CPU restatement of the path over host copies of a workload's tensors."""
+
+    def __init__(self, w, t):
+        import numpy as np
+        import torch
+        from oracle import oracle as O
+        self.O, self.w, self.np = O, w, np
+        code = {"bf16": O.BF16, "f16": O.F16, "f32": O.F32, "fp8": O.FP8}
+        self.dt, self.kvdt = code[w.dtype], code[w.kv_dtype]
+
+        def storage(x, c):
+            x = x.detach().cpu().contiguous()
+            if c == O.F32:
+                return x.numpy()
+            if c == O.FP8:
+                return x.view(torch.uint8).numpy()
+            return x.view(torch.int16).numpy().view(np.uint16)
+
+        self.q = storage(t["q"], self.dt)
+        self.kc, self.vc = storage(t["key_cache"], self.kvdt), storage(t["value_cache"], self.kvdt)
+        self.slopes = None if t["alibi_slopes"] is None else t["alibi_slopes"].cpu().numpy()
+        self.k_scale, self.v_scale = t["k_scale"], t["v_scale"]
+
+    def run(self, n: int) -> float:
+        """One pass over the first n sequences; seconds."""
+        w, O = self.w, self.O
+        t0 = time.perf_counter()
+        O.paged_attention(self.q[:n], self.kc, self.vc, w.block_tables[:n], w.context_lens[:n], w.scale, self.dt,
+                          self.kvdt, w.softcapping, self.slopes, self.k_scale, self.v_scale, naive_f32=True)
+        return time.perf_counter() - t0
+
+    def kv_bytes(self, n: int) -> int:
+        w = self.w
+        return int(w.context_lens[:n].astype(self.np.int64).sum()) * w.num_kv_heads * w.head_size * 2 * w.kv_elem_size
+
+    def seqs_for(self, seconds: float) -> int:
+        n0 = min(4, self.w.num_seqs)
+        self.run(n0)                                   # warms the thread pool up
+        per_seq = self.run(n0) / n0
+        return max(1, min(self.w.num_seqs, int(seconds / max(per_seq, 1e-6))))
+
+
+def cpu_baseline(w, t, budget_s: float = 15.0):
+    """Times the CPU restatement on a bounded sample: the first sequences of the workload, as many as
+    fit the time budget, on every host thread OpenMP offers."""
+    port = CpuPort(w, t)
+    n = port.seqs_for(budget_s / 4)
+    best = min(port.run(n) for _ in range(3))
+    return {"value": round(port.kv_bytes(n) / best / 1e9, 3), "unit": UNIT, "cores": port.O.max_threads(), "kind": "port",
+            "sample": f"first {n} of {w.num_seqs} sequences of the same workload, best of 3 passes "
+                      f"({best:.3f} s per pass), fp32 gather + softmax attention over the paged cache",
+            "host_cpus": os.cpu_count()}
+
+
+def run_reference(args):
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    import torch
+    from attention_rs_b200 import workloads
+    if not torch.cuda.is_available():
+        raise SystemExit("the reference arm draws its inputs from the same seeded device generator as the main arm: "
+                         "run it on the GPU box")
+    w = workloads.decode_workload(args.config, num_seqs=args.num_seqs)
+    dev = torch.device("cuda", local)
+    t = workloads.device_tensors(w, dev)
+    port = CpuPort(w, t)
+    # One step = one pass over a bounded sample of the workload (its first n sequences), sized so that
+    # warm-up plus the timed steps end within --ref-budget seconds.
+    n = port.seqs_for(args.ref_budget / (args.steps + args.warmup))
+    for _ in range(args.warmup):
+        port.run(n)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        port.run(n)
+    dt = time.perf_counter() - t0
+    value = round(port.kv_bytes(n) * args.steps / dt / 1e9, 3)
+    sample = (f"each step = first {n} of {w.num_seqs} sequences of the workload ({port.kv_bytes(n) / 1e6:.1f} MB of KV), "
+              f"fp32 gather + softmax attention over the paged cache")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": describe(w, 1, False),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": port.O.max_threads(), "kind": "port",
+                             "sample": sample, "host_cpus": os.cpu_count()},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation of these operators (its cpu_fwd bails); this is the CPU "
+                    "restatement of its algorithm on every host thread, inputs identical to the main arm"}
+    # Extra context: the reference's own CUDA kernels, compiled unchanged, same inputs, same GPU.
+    try:
+        from oracle import ref_gpu
+        if ref_gpu.available() and w.kv_dtype != "fp8":
+            line["reference_cuda_kernels"] = time_reference_kernels(w, t, ref_gpu)
+    except Exception as exc:  # the CPU number above stands on its own
+        line["reference_cuda_kernels"] = {"unavailable": repr(exc)}
+    print(json.dumps(line), flush=True)
+
+
+def time_reference_kernels(w, t, ref_gpu, reps: int = 20):
+    import torch
+    q = t["q"]
+    mcl = w.max_context_len
+    out = torch.empty_like(q)
+    ws = ref_gpu.v2_workspace(q, mcl)
+    res = {}
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    ms = timed(lambda: ref_gpu.paged_attention_v2(out, q, t["key_cache"], t["value_cache"], t["block_tables"],
+                                                  t["context_lens"], mcl, w.scale, workspace=ws,
+                                                  alibi_slopes=t["alibi_slopes"]))
+    res["v2"] = {"ms_per_step": round(ms, 4), "GBps": round(w.kv_bytes() / ms / 1e6, 1)}
+    if mcl * 4 <= 200 * 1024 and t["alibi_slopes"] is None:
+        ms = timed(lambda: ref_gpu.paged_attention_v1(out, q, t["key_cache"], t["value_cache"], t["block_tables"],
+                                                      t["context_lens"], mcl, w.scale))
+        res["v1"] = {"ms_per_step": round(ms, 4), "GBps": round(w.kv_bytes() / ms / 1e6, 1),
+                     "note": "what the reference's dispatcher picks when num_seqs * num_heads > 512"}
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 4, 5])
+    ap.add_argument("--num-seqs", type=int, default=None,
+                    help="shrink the batch (same shapes and length distribution); for profiler captures only")
+    ap.add_argument("--gather", action="store_true", help="all-gather the outputs inside the timed step (N > 1)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline leg")
+    ap.add_argument("--ref-budget", type=float, default=90.0, help="seconds for all steps of --impl reference")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -120,6 +120,8 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, dtype, c
     """In-place scatter into ``key_cache`` / ``value_cache`` (numpy storage arrays)."""
     cache_dtype = dtype if cache_dtype is None else cache_dtype
     nt, nh, hs = key.shape
+    if nt == 0:
+        return
     assert key.strides[2] == key.itemsize and key.strides[1] == hs * key.itemsize
     assert value.strides[2] == value.itemsize and value.strides[1] == hs * value.itemsize
     nb, nh2, hsx, bs, x = key_cache.shape

@@ -338,7 +338,7 @@ int oracle_paged_attention_naive_f32(float* out, const void* query, const void* 
   const int x = 16 / elem_size((int)kv_dtype);
   const int group = num_heads / num_kv_heads;
   if (kv_dtype != DT_FP8_E4M3) { k_scale = 1.f; v_scale = 1.f; }
-  const int64_t work = (int64_t)num_seqs * num_kv_heads;
+  const int64_t work = (int64_t)num_seqs * num_heads;
 #pragma omp parallel
   {
     const size_t cap = (size_t)(max_context_len > 0 ? max_context_len : 1);
@@ -348,11 +348,13 @@ int oracle_paged_attention_naive_f32(float* out, const void* query, const void* 
     float* qf = (float*)malloc(sizeof(float) * (size_t)head_size);
 #pragma omp for schedule(dynamic, 1)
     for (int64_t w = 0; w < work; ++w) {
-      const int seq = (int)(w / num_kv_heads), kvh = (int)(w % num_kv_heads);
+      /* One work item per (sequence, query head): every query head gathers its own copy of
+       * its kv head's rows, which is what repeat_kv does (src/lib.rs:131-143). */
+      const int seq = (int)(w / num_heads), head = (int)(w % num_heads);
+      const int kvh = head / group;
       int ctx = (int)context_lens[seq];
       if (ctx > max_context_len) ctx = max_context_len;
       const uint32_t* table = block_tables + (int64_t)seq * max_num_blocks_per_seq;
-      /* gather (the "index_select + reshape" a tensor library would do) */
       for (int t = 0; t < ctx; ++t) {
         const int64_t base = (int64_t)table[t / block_size] * kv_block_stride + (int64_t)kvh * kv_head_stride;
         const int off = t % block_size;
@@ -363,8 +365,7 @@ int oracle_paged_attention_naive_f32(float* out, const void* query, const void* 
               load_elem(value_cache, base + (int64_t)d * block_size + off, (int)kv_dtype) * v_scale;
         }
       }
-      for (int g = 0; g < group; ++g) {
-        const int head = kvh * group + g;
+      {
         float* o = out + ((int64_t)seq * num_heads + head) * head_size;
         for (int d = 0; d < head_size; ++d) {
           qf[d] = load_elem(query, (int64_t)seq * q_stride + (int64_t)head * head_size + d, (int)dtype);

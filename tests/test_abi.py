@@ -1,0 +1,169 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares, and
+the host-side operator mirror rejects bad arguments with the reference's messages before touching CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "pagedattention_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b([a-z_][a-z0-9_]*)\s*\([^;{]*\)\s*;", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from attention_rs_b200 import ops
+    return ops.load_library()
+
+
+def test_header_declares_the_reference_ffi():
+    names = declared_functions()
+    for ref in ("call_reshape_and_cache", "paged_attention_v1", "paged_attention_v2"):
+        assert ref in names
+    assert len(names) >= 12
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+
+
+def test_version_and_error_text(lib):
+    assert re.fullmatch(r"\d+\.\d+\.\d+", lib.pa_version().decode())
+    assert isinstance(lib.pa_last_error(), bytes)
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from attention_rs_b200 import ops
+    monkeypatch.setattr(ops, "_lib", None)
+    monkeypatch.setattr(ops, "_LIB_NAME", "libdoes_not_exist.so")
+    with pytest.raises(ops.PagedAttentionError, match="no CPU or PyTorch fallback"):
+        ops.load_library()
+
+
+def test_cpu_tensors_are_refused():
+    import torch
+    import attention_rs_b200 as pa
+    q = torch.zeros((1, 4, 64), dtype=torch.bfloat16)
+    kc = torch.zeros((2, 2, 8, 16, 8), dtype=torch.bfloat16)
+    vc = torch.zeros((2, 2, 64, 16), dtype=torch.bfloat16)
+    bt = torch.zeros((1, 2), dtype=torch.int32)
+    cl = torch.zeros((1,), dtype=torch.int32)
+    with pytest.raises(pa.PagedAttentionError, match="no CPU path"):
+        pa.paged_attention(q, kc, vc, bt, cl, None, 16, 0.125)
+    with pytest.raises(pa.PagedAttentionError, match="no CPU path"):
+        pa.reshape_and_cache(q, q, kc, vc, torch.zeros((1,), dtype=torch.int64))
+
+
+# ---- validation of the operator mirror, exercised with fake device pointers (nothing is launched)
+
+def desc(shape, dtype, stride=None, data=0x10000):
+    from attention_rs_b200.ops import _Tensor
+    d = _Tensor()
+    d.data, d.dtype, d.rank = data, dtype, len(shape)
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= s
+    st = list(reversed(st)) if stride is None else stride
+    for i, (s, t) in enumerate(zip(shape, st)):
+        d.shape[i], d.stride[i] = s, t
+    return d
+
+
+def attn_args(**over):
+    from attention_rs_b200 import ops
+    a = dict(q=desc((2, 8, 128), ops.BF16), kc=desc((10, 2, 16, 16, 8), ops.BF16), vc=desc((10, 2, 128, 16), ops.BF16),
+             bt=desc((2, 4), ops.U32), cl=desc((2,), ops.U32), slopes=None, mcl=64, out=desc((2, 8, 128), ops.BF16))
+    a.update(over)
+    return a
+
+
+def call_attn(lib, a):
+    ref = lambda d: None if d is None else ctypes.byref(d)
+    rc = lib.pa_paged_attention(ref(a["q"]), ref(a["kc"]), ref(a["vc"]), ref(a["bt"]), ref(a["cl"]), ref(a["slopes"]),
+                                a["mcl"], 0.1, 1.0, 1.0, 1.0, ref(a["out"]), None, 0, 0)
+    return rc, lib.pa_last_error().decode()
+
+
+@pytest.mark.parametrize("over,msg", [
+    (dict(q=None), "null tensor descriptor"),
+    (dict(q=desc((2, 8, 128), 3)), "is not supported"),
+    (dict(q=desc((2, 8, 1, 128), 1)), "expects `q` tensor to be of rank 3"),
+    (dict(kc=desc((10, 2, 16, 128), 1)), "expects `key_cache` tensor to be of rank 5"),
+    (dict(vc=desc((10, 2, 16, 16, 8), 1)), "expects `value_cache` tensor to be of rank 4"),
+    (dict(q=desc((2, 8, 72), 1), out=desc((2, 8, 72), 1)), "`head_size` must be one of 64, 80, 96, 112, 128, 192 or 256"),
+    (dict(bt=desc((3, 4), 16)), "shape mismatch block_tables"),
+    (dict(kc=desc((10, 2, 8, 16, 8), 1)), "shape mismatch value_cache"),
+    (dict(vc=desc((10, 2, 128, 32), 1)), "shape mismatch key_cache"),
+    (dict(cl=desc((3,), 16)), "shape mismatch context_lens"),
+    (dict(bt=desc((2, 4), 17)), "must be u32"),
+    (dict(kc=desc((10, 3, 16, 16, 8), 1), vc=desc((10, 3, 128, 16), 1)), "multiple of num_kv_heads"),
+    (dict(kc=desc((10, 2, 16, 4, 8), 1), vc=desc((10, 2, 128, 4), 1)), "`block_size` must be one of 8, 16 or 32"),
+    (dict(mcl=100), "fewer than max_context_len"),
+    (dict(out=desc((2, 8, 128), 0)), "out must be"),
+    (dict(slopes=desc((7,), 2)), "alibi_slopes must be"),
+    (dict(q=desc((2, 8, 128), 1, stride=[2048, 256, 1])), "contiguous in its last two dimensions"),
+    (dict(kc=desc((10, 2, 16, 16, 8), 3), vc=desc((10, 2, 128, 16), 3)), "chunk width x must be 16"),
+])
+def test_paged_attention_validation(lib, over, msg):
+    rc, text = call_attn(lib, attn_args(**over))
+    assert rc != 0 and msg in text, (rc, text)
+
+
+def reshape_args(**over):
+    from attention_rs_b200 import ops
+    a = dict(k=desc((5, 2, 128), ops.F16), v=desc((5, 2, 128), ops.F16), kc=desc((10, 2, 16, 16, 8), ops.F16),
+             vc=desc((10, 2, 128, 16), ops.F16), slots=desc((5,), ops.I64))
+    a.update(over)
+    return a
+
+
+@pytest.mark.parametrize("over,msg", [
+    (dict(k=desc((5, 256), 0)), "expects input tensors of rank 3"),
+    (dict(kc=desc((10, 2, 128, 16), 0)), "expects `key_cache` tensor to be of rank 5"),
+    (dict(vc=desc((10, 2, 16, 16, 8), 0)), "expects `value_cache` tensor to be of rank 4"),
+    (dict(v=desc((6, 2, 128), 0)), "shape mismatch k"),
+    (dict(kc=desc((10, 4, 16, 16, 8), 0)), "shape mismatch value_cache"),
+    (dict(vc=desc((9, 2, 128, 16), 0)), "shape mismatch key_cache"),
+    (dict(slots=desc((4,), 17)), "shape mismatch slot_mapping"),
+    (dict(slots=desc((5,), 16)), "slot_mapping must be an i64 tensor"),
+    (dict(v=desc((5, 2, 128), 1)), "key and value must share a dtype"),
+    (dict(kc=desc((10, 2, 16, 16, 8), 2), vc=desc((10, 2, 128, 16), 2)), "dtype must match key or be FP8"),
+])
+def test_reshape_and_cache_validation(lib, over, msg):
+    a = reshape_args(**over)
+    rc = lib.pa_reshape_and_cache(ctypes.byref(a["k"]), ctypes.byref(a["v"]), ctypes.byref(a["kc"]), ctypes.byref(a["vc"]),
+                                  ctypes.byref(a["slots"]), 1.0, 1.0, 0)
+    assert rc != 0 and msg in lib.pa_last_error().decode(), lib.pa_last_error()
+
+
+def test_workspace_size_and_partition_rule(lib):
+    # tmp_out + exp_sums + max_logits as the reference allocates them (src/paged_attention.rs:199-203)
+    ns, nh, hs, mcl = 64, 32, 128, 8192
+    parts = 16
+    need = lib.pa_paged_attention_workspace_bytes(ns, nh, hs, mcl, 1)
+    exact = ns * nh * parts * hs * 2 + 2 * ns * nh * parts * 4
+    assert exact <= need <= exact + 3 * 256
+    assert lib.pa_paged_attention_workspace_bytes(ns, nh, hs, 0, 1) == 0
+    assert lib.pa_paged_attention_uses_partitions(ns, nh, 8, 512) == 0
+    assert lib.pa_paged_attention_uses_partitions(ns, nh, 8, 513) == 1
+
+
+def test_ex_entry_points_reject_bad_arguments_without_a_gpu(lib):
+    rc = lib.call_reshape_and_cache_ex(None, None, None, None, None, 4, 2, 64, 16, 8, 128, 128, 1, 1, 1.0, 1.0, 0)
+    assert rc == 1 and b"null pointer" in lib.pa_last_error()
+    rc = lib.call_reshape_and_cache_ex(1, 1, 1, 1, 1, 4, 2, 64, 16, 7, 128, 128, 1, 1, 1.0, 1.0, 0)
+    assert rc == 1
+    rc = lib.call_reshape_and_cache_ex(1, 1, 1, 1, 1, 4, 2, 64, 16, 16, 128, 128, 1, 3, 0.0, 1.0, 0)
+    assert rc == 1 and b"positive" in lib.pa_last_error()
+    assert lib.call_reshape_and_cache_ex(None, None, None, None, None, 0, 2, 64, 16, 8, 128, 128, 1, 1, 1.0, 1.0, 0) == 0
+    tail = [2, 0.1, 1, 1, 16, 64, 2, 8, 128, 4, 1024, 4096, 2048, 1, 1.0]
+    assert lib.paged_attention_v2_ex(1, None, None, None, 1, 1, 1, *tail, None, 1, 1.0, 1.0, 0) == 4   # no workspace
+    assert lib.paged_attention_v1_ex(None, 1, 1, 1, *tail, None, 1, 1.0, 1.0, 0) == 1
