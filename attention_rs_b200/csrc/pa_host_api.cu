@@ -107,6 +107,7 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
     return fail(PA_ERR_INVALID_ARGUMENT, "shape mismatch context_lens %s, expected [%lld]", dims(context_lens).c_str(),
                 (long long)num_seqs);
 
+  if (num_seqs == 0) return PA_OK;
   // Checks the reference leaves to the kernel's assumptions; made explicit here.
   if (x * pa::dtype_size(kv_dtype) != 16)
     return fail(PA_ERR_INVALID_ARGUMENT, "key_cache chunk width x must be 16 / sizeof(cache element), got %lld", (long long)x);
@@ -136,7 +137,6 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
   if (!fits_i32(q->stride[0]) || !fits_i32(key_cache->stride[0]) || !fits_i32(key_cache->stride[1]) ||
       !fits_i32(max_context_len) || !fits_i32(max_blocks))
     return fail(PA_ERR_INVALID_ARGUMENT, "a stride or size does not fit the 32-bit fields of the kernel interface");
-  if (num_seqs == 0) return PA_OK;
 
   const bool want_parts = pa_paged_attention_uses_partitions(num_seqs, num_heads, num_kv_heads, max_context_len) != 0;
   const size_t need = pa_paged_attention_workspace_bytes(num_seqs, num_heads, head_size, max_context_len, q->dtype);
@@ -203,6 +203,7 @@ int pa_reshape_and_cache(const pa_tensor* key, const pa_tensor* value, const pa_
   if (slot_mapping->rank != 1 || slot_mapping->shape[0] != num_tokens)
     return fail(PA_ERR_INVALID_ARGUMENT, "shape mismatch slot_mapping %s, expected [%lld]", dims(slot_mapping).c_str(),
                 (long long)num_tokens);
+  if (num_tokens == 0) return PA_OK;
   // Made explicit here; the reference's kernel assumes them.
   if (head_size % x != 0) return fail(PA_ERR_INVALID_ARGUMENT, "head_size %lld is not a multiple of x %lld", (long long)head_size, (long long)x);
   if (key->stride[2] != 1 || key->stride[1] != head_size || value->stride[2] != 1 || value->stride[1] != head_size)

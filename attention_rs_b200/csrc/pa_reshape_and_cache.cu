@@ -8,7 +8,9 @@
 //   value_cache[num_blocks, num_heads, head_size, block_size].
 //
 // The reference moves one element per thread with 2-byte loads and stores.  Here a
-// CTA takes 32 consecutive tokens:
+// CTA takes up to 32 consecutive tokens and a slice of the (head, dim) columns (few
+// tokens per CTA when the call is small, so that a decode step's handful of tokens
+// still spreads over the SMs):
 //  * keys move as whole 16-byte chunks (x elements), one load and one store each;
 //  * for values the CTA first groups its tokens by destination block.  Along a
 //    value-cache row the tokens of one block are adjacent, so wherever a group
@@ -47,7 +49,7 @@ __global__ void __launch_bounds__(RC_THREADS)
 reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value, D* __restrict__ key_cache,
                          D* __restrict__ value_cache, const int64_t* __restrict__ slot_mapping, int num_tokens,
                          int num_heads, int head_size, int64_t key_stride, int64_t value_stride, float k_scale,
-                         float v_scale) {
+                         float v_scale, int tokens_per_cta) {
   constexpr int X = 16 / sizeof(D);                 // cache elements per 16-byte key chunk
   constexpr int PIECE = X < BS ? X : BS;            // elements of a value row written by one wide store
   constexpr int NPIECE = BS / PIECE;
@@ -57,11 +59,16 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
   __shared__ unsigned g_mask[RC_TOKENS];            // offsets present in group g
   __shared__ signed char g_map[RC_TOKENS][BS];      // offset -> token index within the CTA
   __shared__ int s_ngroups;
+  __shared__ unsigned s_single;                     // tokens that are alone in their block
 
-  const int tok0 = blockIdx.x * RC_TOKENS;
-  const int ntok = min(RC_TOKENS, num_tokens - tok0);
+  const int tok0 = blockIdx.x * tokens_per_cta;
+  const int ntok = min(tokens_per_cta, num_tokens - tok0);
   const int tid = threadIdx.x;
   const int n = num_heads * head_size;
+  // This CTA's slice of the columns: rows [row_lo, row_hi) of the value cache, a multiple of X wide.
+  const int cols_per_cta = ((n / X + gridDim.y - 1) / gridDim.y) * X;
+  const int row_lo = blockIdx.y * cols_per_cta;
+  const int row_hi = min(n, row_lo + cols_per_cta);
 
   if (tid < RC_TOKENS) {
     const int lane = tid;
@@ -81,52 +88,61 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
       if (other == blk && i < leader) leader = i;
     }
     const unsigned leaders = __ballot_sync(0xffffffffu, blk >= 0 && leader == lane);
-    if (lane == 0) s_ngroups = __popc(leaders);
     __syncwarp();
+    int g = -1;
     if (blk >= 0) {
-      const int g = __popc(leaders & ((1u << leader) - 1u));
+      g = __popc(leaders & ((1u << leader) - 1u));
       if (leader == lane) g_blk[g] = blk;
       atomicOr(&g_mask[g], 1u << off);
       g_map[g][off] = static_cast<signed char>(lane);
     }
+    __syncwarp();
+    const unsigned gm = g >= 0 ? g_mask[g] : 0u;
+    const unsigned single = __ballot_sync(0xffffffffu, g >= 0 && (gm & (gm - 1u)) == 0u);
+    if (lane == 0) { s_ngroups = __popc(leaders); s_single = single; }
   }
   __syncthreads();
 
   // ---- keys: one 16-byte chunk of the cache per thread-iteration
-  const int chunks_per_tok = n / X;
   const int cph = head_size / X;  // chunks per head
-  for (int j = 0; j < ntok; ++j) {
-    const int64_t blk = s_blk[j];
-    if (blk < 0) continue;
-    const int off = s_off[j];
-    const S* src = key + (tok0 + j) * key_stride;
-    for (int c = tid; c < chunks_per_tok; c += RC_THREADS) {
-      const int h = c / cph, ci = c % cph;
+  const int chunk_lo = row_lo / X, chunk_hi = row_hi / X;
+  for (int c = chunk_lo + tid; c < chunk_hi; c += RC_THREADS) {
+    const int h = c / cph, ci = c % cph;
+#pragma unroll 4
+    for (int j = 0; j < ntok; ++j) {
+      const int64_t blk = s_blk[j];
+      if (blk < 0) continue;
+      const S* src = key + (tok0 + j) * key_stride + c * X;
       Pack<D, X> outv;
       if constexpr (!QUANT) {
-        outv = *reinterpret_cast<const Pack<D, X>*>(src + c * X);
+        outv = *reinterpret_cast<const Pack<D, X>*>(src);
       } else {
-        const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src + c * X);
+        const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src);
 #pragma unroll
         for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
       }
-      D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + off) * X;
+      D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
       *reinterpret_cast<Pack<D, X>*>(dst) = outv;
     }
   }
 
-  // ---- values: rows of the cache, grouped by destination block
+  // ---- values: rows of the cache
   const int ngroups = s_ngroups;
-  for (int row = tid; row < n; row += RC_THREADS) {
+  const unsigned single = s_single;
+  for (int row = row_lo + tid; row < row_hi; row += RC_THREADS) {
     const S* src = value + tok0 * value_stride + row;
+    // tokens alone in their block: one element each, loads independent of one another
+#pragma unroll 8
+    for (int j = 0; j < ntok; ++j) {
+      if (single & (1u << j))
+        value_cache[(s_blk[j] * n + row) * BS + s_off[j]] = convert_elem<S, D, QUANT>(src[j * value_stride], v_scale);
+    }
+    if (single == (ntok >= 32 ? 0xffffffffu : ((1u << ntok) - 1u))) continue;
+    // blocks that receive several tokens: aligned pieces of the row go out as one wide store
     for (int g = 0; g < ngroups; ++g) {
       const unsigned mask = g_mask[g];
+      if ((mask & (mask - 1u)) == 0u) continue;
       D* dst = value_cache + (g_blk[g] * n + row) * BS;
-      if ((mask & (mask - 1u)) == 0u) {  // a single token in this block
-        const int off = __ffs(mask) - 1;
-        dst[off] = convert_elem<S, D, QUANT>(src[g_map[g][off] * value_stride], v_scale);
-        continue;
-      }
 #pragma unroll
       for (int pc = 0; pc < NPIECE; ++pc) {
         constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
@@ -185,11 +201,20 @@ int launch_typed(const ReshapeArgs& a, cudaStream_t stream) {
                     (a.block_size == 8 || a.block_size == 16 || a.block_size == 32);
   if (a.num_tokens <= 0) return PA_OK;
   if (fast) {
-    const int grid = (a.num_tokens + RC_TOKENS - 1) / RC_TOKENS;
+    // Few tokens (a decode step): one token per CTA and the columns split over several CTAs, so the
+    // call is not serialised on a couple of SMs.  Many tokens (a prefill): 32 per CTA, which lets
+    // consecutive slots of one block leave as wide stores.
+    const int tpc = a.num_tokens >= 2048 ? RC_TOKENS : (a.num_tokens >= 256 ? 4 : 1);
+    const int gx = (a.num_tokens + tpc - 1) / tpc;
+    const int n = a.num_heads * a.head_size;
+    const int max_split = (n / X + RC_THREADS - 1) / RC_THREADS;          // at least one chunk per thread
+    int gy = (592 + gx - 1) / gx;
+    gy = gy < 1 ? 1 : (gy > max_split ? max_split : gy);
+    const dim3 grid(gx, gy);
 #define PA_RC_GO(BS)                                                                                               \
   reshape_and_cache_kernel<S, D, QUANT, BS><<<grid, RC_THREADS, 0, stream>>>(                                      \
       key, value, kc, vc, a.slot_mapping, a.num_tokens, a.num_heads, a.head_size, a.key_stride, a.value_stride,   \
-      a.k_scale, a.v_scale)
+      a.k_scale, a.v_scale, tpc)
     if (a.block_size == 8) PA_RC_GO(8);
     else if (a.block_size == 16) PA_RC_GO(16);
     else PA_RC_GO(32);

@@ -2,8 +2,7 @@
 
 Only the test-suite, the smoke check and the CPU-baseline / reference legs of the
 benchmark import this module.  It loads ``oracle/liboracle.so`` (built from
-``paged_oracle.c`` by ``make -C oracle``) and offers numpy-level helpers plus
-seeded generators of the benchmark workloads.
+``paged_oracle.c`` by ``make -C oracle``) and offers numpy-level helpers.
 
 Array conventions: 16-bit floats travel as ``uint16`` bit patterns, FP8 as
 ``uint8``; fp32 as ``float32``.  dtype codes: 0 = f16, 1 = bf16, 2 = f32
@@ -56,7 +55,7 @@ def lib() -> ctypes.CDLL:
         L.oracle_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, u32, u32, f32, f32]
         attn = [vp, vp, vp, vp, i32, f32, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, u32, u32, f32, vp, f32, f32]
         L.oracle_paged_attention.restype = ctypes.c_int
-        L.oracle_paged_attention.argtypes = attn + [i32]
+        L.oracle_paged_attention.argtypes = attn + [i32, i32]
         L.oracle_paged_attention_naive_f32.restype = ctypes.c_int
         L.oracle_paged_attention_naive_f32.argtypes = attn
         _lib = L
@@ -136,7 +135,7 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, dtype, c
 
 def paged_attention(query, key_cache, value_cache, block_tables, context_lens, scale, dtype, kv_dtype=None,
                     softcapping=1.0, alibi_slopes=None, k_scale=1.0, v_scale=1.0, partition_size=0,
-                    max_context_len=None, naive_f32=False):
+                    max_context_len=None, naive_f32=False, reference_literal_alibi=False):
     """fp32 output [num_seqs, num_heads, head_size] of the oracle's decode attention."""
     kv_dtype = dtype if kv_dtype is None else kv_dtype
     ns, nh, hs = query.shape
@@ -155,7 +154,7 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, s
     if naive_f32:
         rc = lib().oracle_paged_attention_naive_f32(*args)
     else:
-        rc = lib().oracle_paged_attention(*args, partition_size)
+        rc = lib().oracle_paged_attention(*args, partition_size, 1 if reference_literal_alibi else 0)
     if rc != 0:
         raise RuntimeError(f"oracle_paged_attention failed: {rc}")
     return out

@@ -31,6 +31,17 @@
  * sat_e4m3_rn(x / scale) computed with an IEEE fp32 division, and decode reads
  * float(e4m3) * scale.
  *
+ * ALiBi.  The bias of the algorithm is slope * (token - context_len + 1), a value <= 0.
+ * The reference's device code writes exactly that expression
+ * (src/kernels/src/pagedattention.cu:235; same line in its Metal twin,
+ * src/metal-kernels/src/pagedattention.metal:1122) but with context_len declared
+ * uint32_t (:119), so the subtraction is carried out in unsigned arithmetic and wraps:
+ * every token but the last receives a bias near slope * 2^32.  Its C ABI never reaches
+ * that line (alibi_slopes is hard-wired to nullptr, :621-622 and :795-796).  The oracle
+ * implements the signed formula (alibi_mode 0), which is what the product computes, and
+ * can also evaluate the reference's literal unsigned expression (alibi_mode 1) so that the
+ * golden outputs of the reference's kernel templates pin this file for ALiBi as well.
+ *
  * dtype codes follow src/kernels/src/pagedattention.cu:723: 0 = f16, 1 = bf16,
  * 2 = f32; 3 = FP8 E4M3 (cache only).
  */
@@ -203,8 +214,8 @@ typedef struct {
 static softmax_state attend_range(const void* q, int64_t q_off, int dtype, const void* kc, const void* vc,
                                   int kv_dtype, const uint32_t* table, int64_t kv_block_stride,
                                   int64_t kv_head_off, int head_size, int block_size, int x, float scale,
-                                  float softcap, float slope, float k_scale, float v_scale, int ctx, int t0,
-                                  int t1, float* logits, float* qf, double* acc) {
+                                  float softcap, float slope, int alibi_mode, float k_scale, float v_scale,
+                                  int ctx, int t0, int t1, float* logits, float* qf, double* acc) {
   softmax_state st;
   st.m = -INFINITY;
   st.l = 0.f;
@@ -220,7 +231,10 @@ static softmax_state attend_range(const void* q, int64_t q_off, int dtype, const
     }
     float s = scale * (float)dot;
     if (softcap != 1.0f) s = tanhf(s / softcap) * softcap;
-    if (slope != 0.f) s += slope * (float)(t - ctx + 1);
+    if (slope != 0.f) {
+      if (alibi_mode == 0) s += slope * (float)(t - ctx + 1);
+      else s += slope * (float)((uint32_t)t - (uint32_t)ctx + 1u);   /* the reference's literal arithmetic */
+    }
     logits[t - t0] = s;
     if (s > st.m) st.m = s;
   }
@@ -254,7 +268,8 @@ static softmax_state attend_range(const void* q, int64_t q_off, int dtype, const
  *
  * A sequence with context_len == 0 yields zeros (the reference's loops are empty
  * and its accumulators start at zero).
- * alibi_slopes may be NULL.  softcapping == 1.0 means "off"
+ * alibi_slopes may be NULL; alibi_mode 0 = signed bias (the algorithm), 1 = the
+ * reference's literal unsigned expression (see the file header).  softcapping == 1.0 means "off"
  * (src/kernels/src/pagedattention.cu:231-233).
  * x, the key-cache chunk width in elements, is 16 / sizeof(cache element)
  * (src/kernels/src/pagedattention.cu:192).
@@ -265,7 +280,8 @@ int oracle_paged_attention(float* out, const void* query, const void* key_cache,
                            int32_t num_seqs, int32_t num_heads, int32_t head_size,
                            int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
                            int32_t kv_head_stride, uint32_t dtype, uint32_t kv_dtype, float softcapping,
-                           const float* alibi_slopes, float k_scale, float v_scale, int32_t partition_size) {
+                           const float* alibi_slopes, float k_scale, float v_scale, int32_t partition_size,
+                           int32_t alibi_mode) {
   if (elem_size((int)dtype) == 0 || dtype == DT_FP8_E4M3 || elem_size((int)kv_dtype) == 0) return -1;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return -2;
   const int x = 16 / elem_size((int)kv_dtype);
@@ -303,7 +319,8 @@ int oracle_paged_attention(float* out, const void* query, const void* key_cache,
         const int t1 = t0 + part < ctx ? t0 + part : ctx;
         softmax_state st = attend_range(query, q_off, (int)dtype, key_cache, value_cache, (int)kv_dtype, table,
                                         kv_block_stride, kv_head_off, head_size, block_size, x, scale,
-                                        softcapping, slope, k_scale, v_scale, ctx, t0, t1, logits, qf, acc);
+                                        softcapping, slope, alibi_mode, k_scale, v_scale, ctx, t0, t1, logits, qf,
+                                        acc);
         const float Mn = st.m > M ? st.m : M;
         const double a = exp((double)M - (double)Mn), b = exp((double)st.m - (double)Mn);
         for (int d = 0; d < head_size; ++d) tot[d] = tot[d] * a + acc[d] * b;
