@@ -1,0 +1,57 @@
+//! FFI declarations for libpagedattention_b200 (replaces src/kernels/src/ffi.rs:4-73 of the
+//! reference; the three first prototypes are unchanged, the rest are additions).
+//! NOT COMPILED in the environment this repository was developed in.
+use core::ffi::{c_int, c_long, c_void};
+
+#[allow(dead_code)]
+extern "C" {
+    // ---- unchanged signatures: drop-in for the reference's symbols
+    pub fn call_reshape_and_cache(
+        key: *const c_void, value: *const c_void, key_cache: *const c_void, value_cache: *const c_void,
+        slot_mapping: *const c_long, num_tokens: c_int, num_heads: c_int, head_size: c_int, block_size: c_int,
+        x: c_int, key_stride: c_int, value_stride: c_int, dtype: u32, stream: i64,
+    );
+    pub fn paged_attention_v1(
+        out: *const c_void, query: *const c_void, key_cache: *const c_void, value_cache: *const c_void,
+        num_kv_heads: c_int, scale: f32, block_tables: *const c_int, context_lens: *const c_int,
+        block_size: c_int, max_context_len: c_int, num_seqs: c_int, num_heads: c_int, head_size: c_int,
+        max_num_blocks_per_seq: c_int, q_stride: c_int, kv_block_stride: c_int, kv_head_stride: c_int,
+        dtype: u32, softscapping: f32, stream: i64,
+    );
+    pub fn paged_attention_v2(
+        out: *const c_void, exp_sums: *const f32, max_logits: *const f32, tmp_out: *const c_void,
+        query: *const c_void, key_cache: *const c_void, value_cache: *const c_void, num_kv_heads: c_int,
+        scale: f32, block_tables: *const c_int, context_lens: *const c_int, block_size: c_int,
+        max_context_len: c_int, num_seqs: c_int, num_heads: c_int, head_size: c_int,
+        max_num_blocks_per_seq: c_int, q_stride: c_int, kv_block_stride: c_int, kv_head_stride: c_int,
+        dtype: u32, softscapping: f32, stream: i64,
+    );
+
+    // ---- additions: ALiBi slopes, FP8-E4M3 cache (dtype code 3) with per-tensor scales, status codes
+    pub fn call_reshape_and_cache_ex(
+        key: *const c_void, value: *const c_void, key_cache: *mut c_void, value_cache: *mut c_void,
+        slot_mapping: *const i64, num_tokens: c_int, num_heads: c_int, head_size: c_int, block_size: c_int,
+        x: c_int, key_stride: c_int, value_stride: c_int, dtype: u32, cache_dtype: u32, k_scale: f32,
+        v_scale: f32, stream: i64,
+    ) -> c_int;
+    pub fn paged_attention_v1_ex(
+        out: *mut c_void, query: *const c_void, key_cache: *const c_void, value_cache: *const c_void,
+        num_kv_heads: c_int, scale: f32, block_tables: *const u32, context_lens: *const u32, block_size: c_int,
+        max_context_len: c_int, num_seqs: c_int, num_heads: c_int, head_size: c_int,
+        max_num_blocks_per_seq: c_int, q_stride: c_int, kv_block_stride: c_int, kv_head_stride: c_int,
+        dtype: u32, softscapping: f32, alibi_slopes: *const f32, kv_cache_dtype: u32, k_scale: f32,
+        v_scale: f32, stream: i64,
+    ) -> c_int;
+    pub fn paged_attention_v2_ex(
+        out: *mut c_void, exp_sums: *mut f32, max_logits: *mut f32, tmp_out: *mut c_void, query: *const c_void,
+        key_cache: *const c_void, value_cache: *const c_void, num_kv_heads: c_int, scale: f32,
+        block_tables: *const u32, context_lens: *const u32, block_size: c_int, max_context_len: c_int,
+        num_seqs: c_int, num_heads: c_int, head_size: c_int, max_num_blocks_per_seq: c_int, q_stride: c_int,
+        kv_block_stride: c_int, kv_head_stride: c_int, dtype: u32, softscapping: f32,
+        alibi_slopes: *const f32, kv_cache_dtype: u32, k_scale: f32, v_scale: f32, stream: i64,
+    ) -> c_int;
+    pub fn pa_paged_attention_uses_partitions(
+        num_seqs: i64, num_heads: i64, num_kv_heads: i64, max_context_len: i64,
+    ) -> c_int;
+    pub fn pa_last_error() -> *const core::ffi::c_char;
+}

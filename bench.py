@@ -36,9 +36,11 @@ METRIC = "paged_decode_attention_effective_kv_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the main decode kernel for one launch of the
-# headline workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {2: None}
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of the decode kernel, from the ncu
+# capture summarised in profiles/paged_decode_mma_bf16_d128_bs16_ncu_full_16seq.md (a 16-sequence slice of
+# the headline workload: 357.17 MB read + 4.33 MB written for 356.53 MB of KV).  Traffic grows in
+# proportion to the KV bytes processed, so a launch's traffic is this ratio times its algorithmic bytes.
+NCU_TRAFFIC_RATIO = {2: 1.0139}
 
 
 def measured_peak():
@@ -262,7 +264,8 @@ def run_ours(args):
             "gpu_launches": args.steps * 2,
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4), "peak_kind": f"of {peak_kind}",
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(args.config),
+                         "traffic": (int(w.kv_bytes() * NCU_TRAFFIC_RATIO[args.config])
+                                     if args.config in NCU_TRAFFIC_RATIO else None),
                          "algorithmic_bytes_per_launch": w.kv_bytes(),
                          "timed": "CUDA events around each step's launches (decode kernel + partition merge)"},
             "clocks": clocks,
