@@ -1,0 +1,85 @@
+// paged_attention_v2_static: the partitioned decode path for callers that can hand
+// over no scratch memory.
+//
+// paged_attention_v2 needs three scratch buffers (tmp_out, exp_sums, max_logits)
+// and expects its caller to allocate them.  Some hosts cannot: an engine that gave
+// every free byte of the device to its KV-cache pool at start-up has nothing left to
+// cudaMalloc from, and a serving loop may forbid cudaMalloc outright because the call
+// synchronises the whole device.  For them this entry point keeps the scratch in a
+// fixed array inside the library image.  The price is stated here once: every GPU
+// that loads the library carries PA_STATIC_SCRATCH_BYTES of it until the process
+// exits, and problems whose scratch would not fit are refused.
+#include "pa_common.cuh"
+#include "pa_launch.h"
+
+namespace {
+
+// Device-resident scratch.  In host code this name is only a handle for the runtime's
+// symbol lookup, never an address a kernel may be given.
+static __device__ __align__(256) unsigned char g_static_scratch[PA_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the current device, resolved on first use.
+unsigned char* static_scratch_address() {
+  static unsigned char* cache[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cache[dev] == nullptr) {
+    unsigned char* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      pa::fail(PA_ERR_CUDA, "cannot resolve the static scratch array: %s", cudaGetErrorString(err));
+      return nullptr;
+    }
+    cache[dev] = ptr;
+  }
+  return cache[dev];
+}
+
+int64_t round_up_256(int64_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" {
+
+size_t pa_static_scratch_needed(int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_context_len,
+                                uint32_t dtype) {
+  const int64_t parts = (static_cast<int64_t>(max_context_len) + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE;
+  if (num_seqs <= 0 || num_heads <= 0 || head_size <= 0 || parts <= 0) return 0;
+  const int64_t slots = static_cast<int64_t>(num_seqs) * num_heads * parts;
+  return static_cast<size_t>(round_up_256(slots * head_size * pa::dtype_size(dtype)) + 2 * round_up_256(slots * 4));
+}
+
+int paged_attention_v2_static(void* out, const void* query, const void* key_cache, const void* value_cache,
+                              int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                              const uint32_t* context_lens, int32_t block_size, int32_t max_context_len,
+                              int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq,
+                              int32_t q_stride, int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype,
+                              float softscapping, const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale,
+                              float v_scale, int64_t stream) {
+  if (num_seqs == 0) return PA_OK;
+  if (num_seqs < 0 || num_heads <= 0 || head_size <= 0 || max_context_len < 0)
+    return pa::fail(PA_ERR_INVALID_ARGUMENT, "bad sizes passed to paged_attention_v2_static");
+  if (pa::dtype_size(dtype) == 0 || dtype == PA_DTYPE_FP8_E4M3)
+    return pa::fail(PA_ERR_UNSUPPORTED, "query dtype code %u not supported", dtype);
+  const size_t need = pa_static_scratch_needed(num_seqs, num_heads, head_size, max_context_len, dtype);
+  if (need > static_cast<size_t>(PA_STATIC_SCRATCH_BYTES))
+    return pa::fail(PA_ERR_WORKSPACE,
+                    "paged_attention_v2_static: this problem needs %zu bytes of scratch, the built-in array holds %zu; "
+                    "use paged_attention_v2 with caller-provided buffers",
+                    need, static_cast<size_t>(PA_STATIC_SCRATCH_BYTES));
+  unsigned char* base = static_scratch_address();
+  if (base == nullptr) return PA_ERR_CUDA;
+  // Carve the array exactly like a caller of paged_attention_v2 would size its buffers.  Nothing in it
+  // has to start at zero: the merge step reads only the slots the partition kernel wrote in this call.
+  const int64_t parts = (static_cast<int64_t>(max_context_len) + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE;
+  const int64_t slots = static_cast<int64_t>(num_seqs) * num_heads * (parts > 0 ? parts : 1);
+  void* tmp_out = base;
+  float* exp_sums = reinterpret_cast<float*>(base + round_up_256(slots * head_size * pa::dtype_size(dtype)));
+  float* max_logits = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(exp_sums) + round_up_256(slots * 4));
+  return paged_attention_v2_ex(out, exp_sums, max_logits, tmp_out, query, key_cache, value_cache, num_kv_heads, scale,
+                               block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
+                               max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
+                               alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
+}
+
+}  // extern "C"

@@ -60,6 +60,10 @@ def load_library() -> ctypes.CDLL:
     L.paged_attention_v1_ex.argtypes = [vp, vp, vp, vp] + tail + [vp, u32, f32, f32, i64]
     L.paged_attention_v2_ex.restype = ctypes.c_int
     L.paged_attention_v2_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.paged_attention_v2_static.restype = ctypes.c_int
+    L.paged_attention_v2_static.argtypes = [vp, vp, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.pa_static_scratch_needed.restype = ctypes.c_size_t
+    L.pa_static_scratch_needed.argtypes = [i32, i32, i32, i32, u32]
     L.pa_paged_attention.restype = ctypes.c_int
     L.pa_paged_attention.argtypes = [tp, tp, tp, tp, tp, tp, i64, f32, f32, f32, f32, tp, vp, ctypes.c_size_t, i64]
     L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t

@@ -129,6 +129,37 @@ int paged_attention_v2_ex(void* out, float* exp_sums, float* max_logits, void* t
                           int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
                           uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream);
 
+/* Size of the scratch array built into the library for paged_attention_v2_static
+ * (16 MiB; held on every GPU that loads the library, until the process exits). */
+#define PA_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+
+/* paged_attention_v2_ex without the three scratch arguments.  This entry point has no
+ * counterpart in the reference.  It is for hosts that cannot provide scratch memory: an
+ * engine that handed all free device memory to its KV-cache pool at start-up, or a
+ * serving loop that bans cudaMalloc because that call synchronises the device.  The
+ * scratch lives in a fixed PA_STATIC_SCRATCH_BYTES array inside the library; the call
+ * itself allocates and frees nothing.
+ *   - Problems needing more than the array holds are refused with PA_ERR_WORKSPACE
+ *     (pa_static_scratch_needed() gives the figure: roughly num_seqs * num_heads *
+ *     ceil(max_context_len / 512) * (head_size * sizeof(query element) + 8) bytes).
+ *   - The first call on each device looks the array's device address up (with that
+ *     device current).  Make that first call outside any stream capture.
+ *   - All calls on one device share the one array and it keeps the previous call's
+ *     contents (nothing in it needs clearing).  Two calls that can overlap on the GPU,
+ *     e.g. on different streams, race on it: serialise them or use paged_attention_v2. */
+int paged_attention_v2_static(void* out, const void* query, const void* key_cache, const void* value_cache,
+                              int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                              const uint32_t* context_lens, int32_t block_size, int32_t max_context_len,
+                              int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq,
+                              int32_t q_stride, int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype,
+                              float softscapping, const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale,
+                              float v_scale, int64_t stream);
+
+/* Bytes of the built-in array a call of paged_attention_v2_static with these sizes would use
+ * (0 for empty problems).  No counterpart in the reference. */
+size_t pa_static_scratch_needed(int32_t num_seqs, int32_t num_heads, int32_t head_size, int32_t max_context_len,
+                                uint32_t dtype);
+
 /* ------------------------------------------------------------------------------------------
  * 3. Host-side mirror of the reference's Rust operators
  * ---------------------------------------------------------------------------------------- */
@@ -164,8 +195,8 @@ size_t pa_paged_attention_workspace_bytes(int64_t num_seqs, int64_t num_heads, i
 
 /* 1 if the dispatcher would take the partitioned (v2) path for these sizes when a
  * workspace is available, else 0.  The reference's rule is at
- * src/paged_attention.rs:158-161; this library uses its own (see DESIGN notes in
- * the source). */
+ * src/paged_attention.rs:158-161; this library uses its own, stated beside the
+ * function's definition. */
 int pa_paged_attention_uses_partitions(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
                                        int64_t max_context_len);
 
