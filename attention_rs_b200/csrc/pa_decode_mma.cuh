@@ -25,10 +25,14 @@
 //  * PV: A = P straight from those registers, B = V with k = token.  Because lane
 //    q owns tokens 4q..4q+3 its B fragment is one 8-byte shared load from the V
 //    row (16-bit cache) or one 4-byte word (FP8 cache), conflict-free.
-//  * FP8 cache: bytes are widened to f16 with cvt.e4m3x2 on the way into the MMA
-//    and the query is converted to f16 once; scales are applied to the fp32 logits
-//    and to the fp32 output.
+//  * FP8 cache: the tiles feed m16n8k32 E4M3 MMAs directly (no per-element widening, which would
+//    make the kernel instruction-bound).  The other operand is split in two FP8 terms so that
+//    nothing is lost to its 3-bit mantissa: each query row is scaled to the E4M3 range and written
+//    as head + tail (two MMAs per tile), and so are the probabilities (scaled by 2^8).  The row
+//    scales, k_scale and v_scale are applied to the fp32 logits and the fp32 output.
 #pragma once
+
+#include <cooperative_groups.h>
 
 #include <type_traits>
 
@@ -53,14 +57,24 @@ struct DecodeParams {
   int num_seqs, num_heads, num_kv_heads, group;
   int max_num_blocks_per_seq, max_parts, q_stride;
   int partition_size;         // 0: the CTA (or cluster) covers the whole context
+  int cluster;                // single pass only: CTAs per (sequence, kv head) that split the context (1 = one CTA)
   float scale, softcap, k_scale, v_scale;
 };
 
 template <typename T, bool FP8, int HEAD, int BS>
 struct DecodeCfg {
-  using MT = std::conditional_t<FP8, __half, T>;  // MMA input type
+  using MT = T;  // input type of the 16-bit MMAs (the FP8 path uses E4M3 MMAs instead)
   static constexpr int ES = FP8 ? 1 : 2;
-  static constexpr int SB = BS >= 16 ? 1 : 16 / BS;  // physical blocks per stage
+#ifndef PA_STAGE_TOKENS_16BIT
+#define PA_STAGE_TOKENS_16BIT 16
+#endif
+#ifndef PA_STAGE_TOKENS_FP8
+#define PA_STAGE_TOKENS_FP8 32
+#endif
+  // Tokens per stage: at least one physical block and one 16-token MMA tile.  An FP8 stage takes 32
+  // tokens so that it carries as many bytes, and as much independent work per warp, as a 16-bit one.
+  static constexpr int STOK_MIN = FP8 ? PA_STAGE_TOKENS_FP8 : PA_STAGE_TOKENS_16BIT;
+  static constexpr int SB = BS >= STOK_MIN ? 1 : STOK_MIN / BS;  // physical blocks per stage
   static constexpr int STOK = BS * SB;               // tokens per stage
   static constexpr int TT = STOK / 16;               // 16-token tiles per stage
   static constexpr int TILE_BYTES = HEAD * BS * ES;  // one block's K tile (V tile is the same size)
@@ -79,7 +93,8 @@ struct DecodeCfg {
   static constexpr int THREADS = NW * WARP;
   static constexpr int RING_BYTES = NW * STAGES * STAGE_BYTES;
   static constexpr int ROW_F = HEAD + 8;  // padded fp32 row of the merge buffer
-  static constexpr int MERGE_BYTES = NW * 16 * ROW_F * 4 + NW * 16 * 2 * 4;
+  static constexpr int WARP_MERGE_BYTES = NW * 16 * ROW_F * 4 + NW * 16 * 2 * 4;  // per-warp (acc, m, l)
+  static constexpr int MERGE_BYTES = WARP_MERGE_BYTES + 16 * ROW_F * 4 + 16 * 2 * 4;  // + the CTA's own result (cluster mode)
   static constexpr int DATA_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
   static constexpr int BAR_BYTES = NW * STAGES * 2 * 8;
   static constexpr int SMEM_BYTES = DATA_BYTES + BAR_BYTES + 128;  // +128: manual alignment slack
@@ -94,25 +109,35 @@ paged_decode_mma_kernel(const DecodeParams p) {
   using MT = typename C::MT;
   constexpr int NW = C::NW, STAGES = C::STAGES, SB = C::SB, STOK = C::STOK, TT = C::TT;
   constexpr int TILE_BYTES = C::TILE_BYTES, STAGE_BYTES = C::STAGE_BYTES;
-  constexpr int KSTEPS = HEAD / 16;  // MMA k-steps of QK^T
+  constexpr int KSTEPS = FP8 ? HEAD / 32 : HEAD / 16;  // MMA k-steps of QK^T
   constexpr int NT = HEAD / 8;       // n-tiles of PV
+
+  namespace cg = cooperative_groups;
+  constexpr int PART = PA_PARTITION_SIZE;   // the context is walked in chunks of this many tokens
+  constexpr int SPC = PART / STOK;          // stages per full chunk
+  static_assert(PART % STOK == 0 && SPC >= NW, "a chunk must hold at least one stage per warp");
+
+  // Lets a dependent launch (the partition merge) be scheduled while this grid drains.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int seq = blockIdx.y;
   const int ctx = static_cast<int>(p.context_lens[seq]);
-  const int part = blockIdx.z;
   const int gsplit = (p.group + 15) / 16;               // head sub-groups per kv head (1 unless group > 16)
   const int kvh = blockIdx.x / gsplit;
   const int head0 = kvh * p.group + (blockIdx.x % gsplit) * 16;
   const int nrows = min(16, kvh * p.group + p.group - head0);  // live rows of the M tile
   const bool rows16 = nrows > 8;
   const bool partitioned = p.partition_size > 0;
+  const int csize = partitioned ? 1 : p.cluster;        // CTAs sharing this (sequence, kv head)
+  const int part = blockIdx.z;                          // partition (v2) or rank in the cluster (v1)
 
-  int t_begin = 0, t_end = ctx;
-  if (partitioned) {
-    t_begin = part * p.partition_size;
-    if (t_begin >= ctx) return;  // nothing to do for this partition
-    t_end = min(ctx, t_begin + p.partition_size);
-  }
+  // Chunks of PART tokens owned by this CTA: first, first + cstride, ...  (v2: exactly one.)
+  const int first = (partitioned || csize > 1) ? part : 0;
+  const int cstride = partitioned ? (1 << 20) : csize;
+  const int t_end = partitioned ? min(ctx, (first + 1) * PART) : ctx;
+  const int nchunks_total = (t_end + PART - 1) / PART;
+  const int my_chunks = first < nchunks_total ? (nchunks_total - 1 - first) / cstride + 1 : 0;
+  if (csize == 1 && my_chunks == 0 && partitioned) return;  // nothing to do for this partition
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gi = lane >> 2, qi = lane & 3;
@@ -122,7 +147,7 @@ paged_decode_mma_kernel(const DecodeParams p) {
   const uint32_t ring = smem_addr(smem) + warp * (STAGES * STAGE_BYTES);
   const uint32_t bars = smem_addr(smem) + C::DATA_BYTES + warp * (STAGES * 16);  // [stage]{K,V}
 
-  if (ctx == 0) {
+  if (ctx == 0 && csize == 1) {
     // Empty context: the reference's loops do not run and its accumulators stay zero.
     if (!partitioned) {
       T* o = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head0) * HEAD;
@@ -137,10 +162,17 @@ paged_decode_mma_kernel(const DecodeParams p) {
   }
   __syncwarp();
 
-  // ---- this warp's share of the range: stages warp, warp + NW, ...
-  const int n_stages_cta = (t_end - t_begin + STOK - 1) / STOK;
-  const int n_mine = n_stages_cta > warp ? (n_stages_cta - warp + NW - 1) / NW : 0;
-  const int last_block = (ctx - 1) / BS;  // last physical-block slot of the sequence that holds tokens
+  // ---- this warp's share: in every chunk of the CTA, stages warp, warp + NW, ...
+  const int cnt_full = (SPC - warp + NW - 1) / NW;      // this warp's stages in a full chunk
+  int n_mine = 0;
+  if (my_chunks > 0) {
+    const int lc = first + (my_chunks - 1) * cstride;   // the CTA's last chunk; only it can be short
+    const int lsc = (min(t_end, (lc + 1) * PART) - lc * PART + STOK - 1) / STOK;
+    n_mine = (my_chunks - 1) * cnt_full + (lsc > warp ? (lsc - warp + NW - 1) / NW : 0);
+  }
+  // First token of this warp's local stage (k-th chunk of the CTA, j-th stage of the warp in it).
+  auto tok0_of = [&](int k, int j) { return (first + k * cstride) * PART + (warp + j * NW) * STOK; };
+  const int last_block = ctx > 0 ? (ctx - 1) / BS : 0;  // last block-table slot of the sequence that holds tokens
   const uint32_t* table = p.block_tables + static_cast<int64_t>(seq) * p.max_num_blocks_per_seq;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.kv_head_stride;
   const unsigned char* kc = reinterpret_cast<const unsigned char*>(p.k_cache);
@@ -148,15 +180,12 @@ paged_decode_mma_kernel(const DecodeParams p) {
   const uint64_t policy = policy_evict_first();
 
   // Block-table entries for a window of 32 of this warp's stages live one per lane.
-  // blk(i, b) = table slot of block b of local stage i.
-  auto slot_of = [&](int i, int b) { return (t_begin / BS) + (warp + i * NW) * SB + b; };
   auto load_entries = [&](int round, uint32_t (&e)[SB]) {
     const int i = round * 32 + lane;
+    const int k = min(i / cnt_full, max(my_chunks - 1, 0));
+    const int slot0 = tok0_of(k, i - k * cnt_full) / BS;
 #pragma unroll
-    for (int b = 0; b < SB; ++b) {
-      const int slot = slot_of(i, b);
-      e[b] = (i < n_mine && slot <= last_block) ? table[slot] : 0xffffffffu;
-    }
+    for (int b = 0; b < SB; ++b) e[b] = (i < n_mine && slot0 + b <= last_block) ? table[slot0 + b] : 0xffffffffu;
   };
   uint32_t ent_cur[SB], ent_nxt[SB];
   load_entries(0, ent_cur);
@@ -202,32 +231,74 @@ paged_decode_mma_kernel(const DecodeParams p) {
     if (i < n_mine) issue(i);
 
   // ---- query fragments (A operand), zero rows beyond the group
+  // 16-bit path: qa[j] = the four A registers of k-step j.  FP8 path: qa = head terms, qb = tail terms,
+  // and qinv_* undo the per-row scaling that brought the row into the E4M3 range.
   uint32_t qa[KSTEPS][4];
+  uint32_t qb[FP8 ? KSTEPS : 1][4];
+  float qinv_lo = 1.f, qinv_hi = 1.f;
   {
     const T* qbase = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(seq) * p.q_stride + static_cast<int64_t>(head0) * HEAD;
-    auto ldq = [&](int row, int col) -> uint32_t {  // two consecutive elements as MT pair
-      if (row >= nrows) return 0u;
-      const uint32_t raw = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col);
-      if constexpr (std::is_same<T, MT>::value) {
-        return raw;
-      } else {  // bf16 query, f16 MMA (FP8 cache)
-        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&raw);
-        const float2 f = __bfloat1622float2(v);
-        return pack2<__half>(f.x, f.y);
-      }
-    };
+    if constexpr (!FP8) {
+      auto ldq = [&](int row, int col) -> uint32_t {  // two consecutive elements
+        return row < nrows ? *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col) : 0u;
+      };
 #pragma unroll
-    for (int j = 0; j < KSTEPS; ++j) {
-      if constexpr (!FP8) {
+      for (int j = 0; j < KSTEPS; ++j) {
         qa[j][0] = ldq(gi, 16 * j + 2 * qi);
         qa[j][1] = ldq(gi + 8, 16 * j + 2 * qi);
         qa[j][2] = ldq(gi, 16 * j + 8 + 2 * qi);
         qa[j][3] = ldq(gi + 8, 16 * j + 8 + 2 * qi);
-      } else {  // k-slot permutation matching the byte order of the FP8 chunks
-        qa[j][0] = ldq(gi, 16 * j + 4 * qi);
-        qa[j][1] = ldq(gi + 8, 16 * j + 4 * qi);
-        qa[j][2] = ldq(gi, 16 * j + 4 * qi + 2);
-        qa[j][3] = ldq(gi + 8, 16 * j + 4 * qi + 2);
+      }
+      (void)qb;
+    } else {
+      // This lane's 4-element runs of rows gi and gi + 8: dims 32j + 4q.. and 32j + 16 + 4q..
+      // Two passes over the (tiny, cached) query rows keep the register footprint small: the first finds
+      // each row's largest magnitude, the second scales and splits.
+      auto load4 = [&](int j, int reg, float (&v)[4]) {
+        const int row = gi + (reg & 1) * 8, col = 32 * j + (reg >> 1) * 16 + 4 * qi;
+        uint2 raw = make_uint2(0u, 0u);
+        if (row < nrows) {
+          raw.x = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col);
+          raw.y = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col + 2);
+        }
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = to_f32<T>(e[k]);
+      };
+      float amax_lo = 0.f, amax_hi = 0.f;
+#pragma unroll
+      for (int j = 0; j < KSTEPS; ++j) {
+#pragma unroll
+        for (int reg = 0; reg < 4; ++reg) {
+          float v[4];
+          load4(j, reg, v);
+          const float m4 = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+          if (reg & 1) amax_hi = fmaxf(amax_hi, m4);
+          else amax_lo = fmaxf(amax_lo, m4);
+        }
+      }
+      amax_lo = fmaxf(amax_lo, __shfl_xor_sync(0xffffffffu, amax_lo, 1));
+      amax_lo = fmaxf(amax_lo, __shfl_xor_sync(0xffffffffu, amax_lo, 2));
+      amax_hi = fmaxf(amax_hi, __shfl_xor_sync(0xffffffffu, amax_hi, 1));
+      amax_hi = fmaxf(amax_hi, __shfl_xor_sync(0xffffffffu, amax_hi, 2));
+      // Scale the row so that its largest element sits at 224 (half the E4M3 maximum).
+      const float qs_lo = amax_lo > 0.f && amax_lo < 3.0e38f ? 224.f / amax_lo : 1.f;
+      const float qs_hi = amax_hi > 0.f && amax_hi < 3.0e38f ? 224.f / amax_hi : 1.f;
+      qinv_lo = 1.f / qs_lo;
+      qinv_hi = 1.f / qs_hi;
+#pragma unroll
+      for (int j = 0; j < KSTEPS; ++j) {
+#pragma unroll
+        for (int reg = 0; reg < 4; ++reg) {
+          float v[4];
+          load4(j, reg, v);
+          const float sc = (reg & 1) ? qs_hi : qs_lo;
+          uint32_t h01, t01, h23, t23;
+          split_e4m3x2(v[0] * sc, v[1] * sc, h01, t01);
+          split_e4m3x2(v[2] * sc, v[3] * sc, h23, t23);
+          qa[j][reg] = h01 | (h23 << 16);
+          qb[j][reg] = t01 | (t23 << 16);
+        }
       }
     }
   }
@@ -237,8 +308,8 @@ paged_decode_mma_kernel(const DecodeParams p) {
   uint32_t koff[TT];
   {
     const int mi = lane >> 3, r = lane & 7;
-    const int tile = FP8 ? (mi & 1) : (mi >> 1);     // which n-tile this matrix feeds
-    const int chunk = FP8 ? (mi >> 1) : (mi & 1);    // which 16-byte chunk of the k-step (pair)
+    const int tile = mi >> 1;     // which n-tile this matrix feeds
+    const int chunk = mi & 1;     // which 16-byte chunk of the k-step
     const int tau = 4 * (r >> 1) + (r & 1) + ((((r >> 2) ^ tile) & 1) ? 2 : 0);
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
@@ -246,17 +317,26 @@ paged_decode_mma_kernel(const DecodeParams p) {
       koff[tt] = (ts / BS) * TILE_BYTES + (chunk * BS + (ts % BS)) * 16;
     }
   }
-  // V.  16-bit: one 8-byte load per n-tile at row gi; FP8: ldmatrix rows.
+  // V.  16-bit: one 8-byte load per n-tile at row gi.  FP8: ldmatrix rows; one x4 load brings, for two
+  // n-tiles, the 16-byte halves that hold stage tokens 0-15 and 16-31 (voff8: matrix mi = lane / 8 serves
+  // n-tile mi / 2, half mi % 2).
   uint32_t voff[TT];
+  uint32_t voff8 = 0;
+  if constexpr (FP8) {
+    static_assert(!FP8 || TT == 2, "the FP8 path walks 32-token stages");
+    const int mi = lane >> 3, r = lane & 7, half = mi & 1;
+    const int vb = (half * 16) / BS, vo = (half * 16) % BS;
+    voff8 = (SB + vb) * TILE_BYTES + ((mi >> 1) * 8 + r) * BS + vo;
+  }
 #pragma unroll
   for (int tt = 0; tt < TT; ++tt) {
+    const int vb = (tt * 16) / BS, vo = (tt * 16) % BS;  // block within the stage and token offset in it
     if constexpr (FP8) {
-      const int mi = lane >> 3, r = lane & 7;
-      voff[tt] = SB * TILE_BYTES + (mi * 8 + r) * BS + tt * 16;
+      voff[tt] = 0;
     } else if constexpr (BS >= 16) {
-      voff[tt] = SB * TILE_BYTES + (gi * BS + tt * 16 + 4 * qi) * 2;
+      voff[tt] = (SB + vb) * TILE_BYTES + (gi * BS + vo + 4 * qi) * 2;
     } else {
-      voff[tt] = SB * TILE_BYTES + (qi >> 1) * TILE_BYTES + (gi * BS + (qi & 1) * 4) * 2;
+      voff[tt] = (SB + 2 * tt + (qi >> 1)) * TILE_BYTES + (gi * BS + (qi & 1) * 4) * 2;
     }
   }
   // Tokens (within a 16-token tile) behind this lane's logits: n-tile 0 -> tokA, tokA+1; n-tile 1 -> tokB, tokB+1.
@@ -279,13 +359,15 @@ paged_decode_mma_kernel(const DecodeParams p) {
   for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 
   bool healthy = true;
+  int ck = 0, cj = 0;  // chunk ordinal and stage-within-chunk of local stage i
 
   for (int i = 0; i < n_mine && healthy; ++i) {
     const int s = i % STAGES;
     const uint32_t par = (i / STAGES) & 1;
     const uint32_t stage = ring + s * STAGE_BYTES;
     const uint32_t bk = bars + s * 16, bv = bk + 8;
-    const int stage_tok0 = t_begin + (warp + i * NW) * STOK;
+    const int stage_tok0 = tok0_of(ck, cj);
+    if (++cj == cnt_full) { cj = 0; ++ck; }
 
     // Rotate the block-table window when the stage to be issued this iteration enters a new round.
     if (((i + STAGES) >> 5) > ent_round + 1) {
@@ -298,141 +380,200 @@ paged_decode_mma_kernel(const DecodeParams p) {
     healthy = __all_sync(0xffffffffu, mbar_wait(bk, par, p.status));
     if (!healthy) break;
 
-    // ---------------- logits of up to TT tiles
+#ifdef PA_DEBUG_SKIP_COMPUTE
+    // Measurement aid (never defined in a product build): stream the tiles and do no arithmetic, which
+    // gives the bandwidth ceiling of this access pattern.
+    healthy = __all_sync(0xffffffffu, mbar_wait(bv, par, p.status));
+    if (!healthy) break;
+    __syncwarp();
+    if (i + STAGES < n_mine) issue(i + STAGES);
+    continue;
+#endif
+    // ---------------- logits of the stage's tiles (independent MMA chains: they overlap)
     float sc[TT][2][4];
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) sc[tt][h][0] = sc[tt][h][1] = sc[tt][h][2] = sc[tt][h][3] = 0.f;
-      if (stage_tok0 + tt * 16 < t_end) {
-        if constexpr (!FP8) {
+    }
+    if constexpr (!FP8) {
 #pragma unroll
-          for (int j = 0; j < KSTEPS; ++j) {
+      for (int j = 0; j < KSTEPS; ++j) {
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+          if (TT == 1 || stage_tok0 + tt * 16 < t_end) {
             uint32_t r0, r1, r2, r3;
             ldmatrix_x4(stage + koff[tt] + j * (2 * BS * 16), r0, r1, r2, r3);
             mma16816<MT>(sc[tt][0], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r0, r1);
             mma16816<MT>(sc[tt][1], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r2, r3);
           }
-        } else {
+        }
+      }
+    } else {
 #pragma unroll
-          for (int j = 0; j < KSTEPS; j += 2) {
+      for (int j = 0; j < KSTEPS; ++j) {
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+          if (stage_tok0 + tt * 16 < t_end) {
             uint32_t r0, r1, r2, r3;
-            ldmatrix_x4(stage + koff[tt] + (j / 2) * (2 * BS * 16), r0, r1, r2, r3);
-            mma16816<MT>(sc[tt][0], qa[j][0], qa[j][1], qa[j][2], qa[j][3], e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
-            mma16816<MT>(sc[tt][1], qa[j][0], qa[j][1], qa[j][2], qa[j][3], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
-            mma16816<MT>(sc[tt][0], qa[j + 1][0], qa[j + 1][1], qa[j + 1][2], qa[j + 1][3], e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
-            mma16816<MT>(sc[tt][1], qa[j + 1][0], qa[j + 1][1], qa[j + 1][2], qa[j + 1][3], e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+            ldmatrix_x4(stage + koff[tt] + j * (2 * BS * 16), r0, r1, r2, r3);
+            mma16832_e4m3(sc[tt][0], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r0, r1);
+            mma16832_e4m3(sc[tt][1], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r2, r3);
+            mma16832_e4m3(sc[tt][0], qb[j][0], qb[j][1], qb[j][2], qb[j][3], r0, r1);
+            mma16832_e4m3(sc[tt][1], qb[j][0], qb[j][1], qb[j][2], qb[j][3], r2, r3);
           }
         }
       }
     }
 
-    // ---------------- online softmax, per tile
-    uint32_t pa_lo[TT][2], pa_hi[TT][2];  // P fragments: [tile][k-lo / k-hi]
+    // ---------------- online softmax over the whole stage (one max / one rescale per stage)
+    // x[tt][0..3]: logits (log2 domain) of tokens tokA, tokA+1, tokB, tokB+1 of tile tt; -inf when masked.
+    auto logits_of = [&](int rowsel, float slope, float rowscale, float (&x)[TT][4]) {
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const int ta = stage_tok0 + tt * 16 + tokA, tb = stage_tok0 + tt * 16 + tokB;
+        float x0 = sc[tt][0][rowsel], x1 = sc[tt][0][rowsel + 1], x2 = sc[tt][1][rowsel], x3 = sc[tt][1][rowsel + 1];
+        if (plain) {
+          const float f = qk_scale_log2 * rowscale;
+          x0 *= f; x1 *= f; x2 *= f; x3 *= f;
+        } else {
+          const float f = qk_scale * rowscale;
+          x0 *= f; x1 *= f; x2 *= f; x3 *= f;
+          if (p.softcap != 1.0f) {
+            const float inv = 1.0f / p.softcap;
+            x0 = tanh_approx(x0 * inv) * p.softcap; x1 = tanh_approx(x1 * inv) * p.softcap;
+            x2 = tanh_approx(x2 * inv) * p.softcap; x3 = tanh_approx(x3 * inv) * p.softcap;
+          }
+          x0 = (x0 + slope * static_cast<float>(ta - ctx + 1)) * LOG2E;
+          x1 = (x1 + slope * static_cast<float>(ta + 1 - ctx + 1)) * LOG2E;
+          x2 = (x2 + slope * static_cast<float>(tb - ctx + 1)) * LOG2E;
+          x3 = (x3 + slope * static_cast<float>(tb + 1 - ctx + 1)) * LOG2E;
+        }
+        x[tt][0] = ta < t_end ? x0 : -INFINITY;
+        x[tt][1] = ta + 1 < t_end ? x1 : -INFINITY;
+        x[tt][2] = tb < t_end ? x2 : -INFINITY;
+        x[tt][3] = tb + 1 < t_end ? x3 : -INFINITY;
+      }
+    };
+    auto row_max = [&](const float (&x)[TT][4]) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) mx = fmaxf(mx, fmaxf(fmaxf(x[tt][0], x[tt][1]), fmaxf(x[tt][2], x[tt][3])));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      return fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    };
+    // P fragments.  16-bit path: pa_*[tile][k-lo / k-hi]; lane q pairs tokens (4q, 4q+1) with V's low word and
+    // (4q+2, 4q+3) with its high word.  FP8 path: pa_*[tile][head / tail], each register the four bytes of
+    // tokens 4q..4q+3; probabilities carry a factor 2^8 (kPBias) that cancels between numerator and denominator.
+    constexpr float kPBias = FP8 ? 8.f : 0.f;
+    uint32_t pa_lo[TT][2], pa_hi[TT][2];
+    auto probs = [&](const float (&x)[TT][4], float m, float& l, uint32_t (&pa)[TT][2]) {
+      float sum = 0.f;
+      const float mb = m - kPBias;
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const float p0 = exp2_approx(x[tt][0] - mb), p1 = exp2_approx(x[tt][1] - mb);
+        const float p2 = exp2_approx(x[tt][2] - mb), p3 = exp2_approx(x[tt][3] - mb);
+        sum += (p0 + p1) + (p2 + p3);
+        if constexpr (!FP8) {
+          const uint32_t pA = pack2<MT>(p0, p1), pB = pack2<MT>(p2, p3);
+          pa[tt][0] = (qi & 2) ? pB : pA;
+          pa[tt][1] = (qi & 2) ? pA : pB;
+        } else {
+          uint32_t hA, tA, hB, tB;
+          split_e4m3x2(p0, p1, hA, tA);   // tokens tokA, tokA + 1
+          split_e4m3x2(p2, p3, hB, tB);   // tokens tokB, tokB + 1
+          pa[tt][0] = (qi & 2) ? (hB | (hA << 16)) : (hA | (hB << 16));
+          pa[tt][1] = (qi & 2) ? (tB | (tA << 16)) : (tA | (tB << 16));
+        }
+      }
+      l += sum;
+    };
+    float x_lo[TT][4], x_hi[TT][4];
+    logits_of(0, slope_lo, qinv_lo, x_lo);
+    float mn_lo = fmaxf(m_lo, row_max(x_lo)), mn_hi = m_hi;   // finite: the stage's first token is valid
+    if (rows16) {
+      logits_of(2, slope_hi, qinv_hi, x_hi);
+      mn_hi = fmaxf(m_hi, row_max(x_hi));
+    }
+    // Rescale what earlier stages accumulated only when some row's running maximum moved.
+    if (__any_sync(0xffffffffu, mn_lo > m_lo || mn_hi > m_hi)) {
+      const float corr_lo = exp2_approx(m_lo - mn_lo);
+      l_lo *= corr_lo;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        acc[n][0] *= corr_lo;
+        acc[n][1] *= corr_lo;
+      }
+      if (rows16) {
+        const float corr_hi = exp2_approx(m_hi - mn_hi);
+        l_hi *= corr_hi;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          acc[n][2] *= corr_hi;
+          acc[n][3] *= corr_hi;
+        }
+      }
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+    }
+    probs(x_lo, m_lo, l_lo, pa_lo);
+    if (rows16) {
+      probs(x_hi, m_hi, l_hi, pa_hi);
+    } else {
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) pa_hi[tt][0] = pa_hi[tt][1] = 0u;
+    }
+
+    // ---------------- PV
+    healthy = __all_sync(0xffffffffu, mbar_wait(bv, par, p.status));
+    if (!healthy) break;
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
       const int tile_tok0 = stage_tok0 + tt * 16;
-      pa_lo[tt][0] = pa_lo[tt][1] = pa_hi[tt][0] = pa_hi[tt][1] = 0u;
-      if (tile_tok0 < t_end) {
-        const int ta = tile_tok0 + tokA, tb = tile_tok0 + tokB;
-        const bool v0 = ta < t_end, v1 = ta + 1 < t_end, v2 = tb < t_end, v3 = tb + 1 < t_end;
-        auto row = [&](float x0, float x1, float x2, float x3, float slope, float& m, float& l, float& corr,
-                       uint32_t& pA, uint32_t& pB) {
-          if (plain) {
-            x0 *= qk_scale_log2; x1 *= qk_scale_log2; x2 *= qk_scale_log2; x3 *= qk_scale_log2;
-          } else {
-            x0 *= qk_scale; x1 *= qk_scale; x2 *= qk_scale; x3 *= qk_scale;
-            if (p.softcap != 1.0f) {
-              const float inv = 1.0f / p.softcap;
-              x0 = tanh_approx(x0 * inv) * p.softcap; x1 = tanh_approx(x1 * inv) * p.softcap;
-              x2 = tanh_approx(x2 * inv) * p.softcap; x3 = tanh_approx(x3 * inv) * p.softcap;
-            }
-            x0 = (x0 + slope * static_cast<float>(ta - ctx + 1)) * LOG2E;
-            x1 = (x1 + slope * static_cast<float>(ta + 1 - ctx + 1)) * LOG2E;
-            x2 = (x2 + slope * static_cast<float>(tb - ctx + 1)) * LOG2E;
-            x3 = (x3 + slope * static_cast<float>(tb + 1 - ctx + 1)) * LOG2E;
+      if (TT == 1 || tile_tok0 < t_end) {
+        // Cache memory past the context may hold anything (NaNs included): clear those V words.
+        const bool partial = tile_tok0 + 16 > t_end;
+        const int vt = tile_tok0 + 4 * qi;  // first of this lane's four tokens
+        if constexpr (!FP8) {
+          uint32_t mk0 = 0xffffffffu, mk1 = 0xffffffffu;
+          if (partial) {
+            mk0 = (vt < t_end ? 0x0000ffffu : 0u) | (vt + 1 < t_end ? 0xffff0000u : 0u);
+            mk1 = (vt + 2 < t_end ? 0x0000ffffu : 0u) | (vt + 3 < t_end ? 0xffff0000u : 0u);
           }
-          x0 = v0 ? x0 : -INFINITY; x1 = v1 ? x1 : -INFINITY; x2 = v2 ? x2 : -INFINITY; x3 = v3 ? x3 : -INFINITY;
-          float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          const float mn = fmaxf(m, mx);   // finite: token tile_tok0 is valid
-          corr = exp2_approx(m - mn);
-          const float p0 = exp2_approx(x0 - mn), p1 = exp2_approx(x1 - mn);
-          const float p2 = exp2_approx(x2 - mn), p3 = exp2_approx(x3 - mn);
-          l = l * corr + ((p0 + p1) + (p2 + p3));
-          m = mn;
-          pA = pack2<MT>(p0, p1);
-          pB = pack2<MT>(p2, p3);
-        };
-        float corr_lo, corr_hi = 1.f;
-        uint32_t pA, pB;
-        row(sc[tt][0][0], sc[tt][0][1], sc[tt][1][0], sc[tt][1][1], slope_lo, m_lo, l_lo, corr_lo, pA, pB);
-        // lane q pairs (tokens 4q,4q+1) with V's low word and (4q+2,4q+3) with its high word
-        pa_lo[tt][0] = (qi & 2) ? pB : pA;
-        pa_lo[tt][1] = (qi & 2) ? pA : pB;
-        if (rows16) {
-          row(sc[tt][0][2], sc[tt][0][3], sc[tt][1][2], sc[tt][1][3], slope_hi, m_hi, l_hi, corr_hi, pA, pB);
-          pa_hi[tt][0] = (qi & 2) ? pB : pA;
-          pa_hi[tt][1] = (qi & 2) ? pA : pB;
-        }
-        // Rescale what earlier tiles accumulated to the new running maximum.
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          acc[n][0] *= corr_lo;
-          acc[n][1] *= corr_lo;
-        }
-        if (rows16) {
 #pragma unroll
           for (int n = 0; n < NT; ++n) {
-            acc[n][2] *= corr_hi;
-            acc[n][3] *= corr_hi;
-          }
-        }
-
-        // ---------------- PV of this tile
-        if (tt == 0) {
-          healthy = __all_sync(0xffffffffu, mbar_wait(bv, par, p.status));
-        }
-        if (healthy) {
-          // Validity masks for V words of a partial tile (cache memory past the context may hold NaNs).
-          const bool partial = tile_tok0 + 16 > t_end;
-          const int vt = tile_tok0 + 4 * qi;  // first of this lane's four tokens
-          if constexpr (!FP8) {
-            uint32_t mk0 = 0xffffffffu, mk1 = 0xffffffffu;
-            if (partial) {
-              mk0 = (vt < t_end ? 0x0000ffffu : 0u) | (vt + 1 < t_end ? 0xffff0000u : 0u);
-              mk1 = (vt + 2 < t_end ? 0x0000ffffu : 0u) | (vt + 3 < t_end ? 0xffff0000u : 0u);
-            }
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-              uint32_t b0, b1;
-              lds64(stage + voff[tt] + n * (8 * BS * 2), b0, b1);
-              if (partial) { b0 &= mk0; b1 &= mk1; }
-              mma16816<MT>(acc[n], pa_lo[tt][0], pa_hi[tt][0], pa_lo[tt][1], pa_hi[tt][1], b0, b1);
-            }
-          } else {
-            uint32_t mk = 0xffffffffu;
-            if (partial) {
-              mk = (vt < t_end ? 0x000000ffu : 0u) | (vt + 1 < t_end ? 0x0000ff00u : 0u) |
-                   (vt + 2 < t_end ? 0x00ff0000u : 0u) | (vt + 3 < t_end ? 0xff000000u : 0u);
-            }
-#pragma unroll
-            for (int n = 0; n < NT; n += 4) {
-              uint32_t r[4];
-              ldmatrix_x4(stage + voff[tt] + (n / 4) * (32 * BS), r[0], r[1], r[2], r[3]);
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const uint32_t w = r[u] & mk;
-                mma16816<MT>(acc[n + u], pa_lo[tt][0], pa_hi[tt][0], pa_lo[tt][1], pa_hi[tt][1], e4m3x2_to_f16x2(w),
-                             e4m3x2_to_f16x2(w >> 16));
-              }
-            }
+            uint32_t b0, b1;
+            lds64(stage + voff[tt] + n * (8 * BS * 2), b0, b1);
+            if (partial) { b0 &= mk0; b1 &= mk1; }
+            mma16816<MT>(acc[n], pa_lo[tt][0], pa_hi[tt][0], pa_lo[tt][1], pa_hi[tt][1], b0, b1);
           }
         }
       }
     }
-    if (!healthy) break;
+    if constexpr (FP8) {
+      // One k32 MMA covers the stage's 32 tokens.  Cache bytes past the context may hold anything (NaN
+      // codes included): clear them.  mk[h] masks this lane's four tokens of half h.
+      uint32_t mk[2] = {0xffffffffu, 0xffffffffu};
+      if (stage_tok0 + 32 > t_end) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int vt = stage_tok0 + h * 16 + 4 * qi;
+          mk[h] = (vt < t_end ? 0x000000ffu : 0u) | (vt + 1 < t_end ? 0x0000ff00u : 0u) |
+                  (vt + 2 < t_end ? 0x00ff0000u : 0u) | (vt + 3 < t_end ? 0xff000000u : 0u);
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4(stage + voff8 + (n / 2) * (16 * BS), r0, r1, r2, r3);
+        r0 &= mk[0]; r1 &= mk[1]; r2 &= mk[0]; r3 &= mk[1];
+        mma16832_e4m3(acc[n], pa_lo[0][0], pa_hi[0][0], pa_lo[1][0], pa_hi[1][0], r0, r1);
+        mma16832_e4m3(acc[n + 1], pa_lo[0][0], pa_hi[0][0], pa_lo[1][0], pa_hi[1][0], r2, r3);
+        mma16832_e4m3(acc[n], pa_lo[0][1], pa_hi[0][1], pa_lo[1][1], pa_hi[1][1], r0, r1);
+        mma16832_e4m3(acc[n + 1], pa_lo[0][1], pa_hi[0][1], pa_lo[1][1], pa_hi[1][1], r2, r3);
+      }
+    }
 
     // Stage consumed by every lane: hand it back to the copy engine.
     __syncwarp();
@@ -465,35 +606,83 @@ paged_decode_mma_kernel(const DecodeParams p) {
   __syncthreads();
 
   const float vscale = FP8 ? p.v_scale : 1.0f;
-  for (int idx = threadIdx.x; idx < nrows * (HEAD / 2); idx += C::THREADS) {
-    const int r = idx / (HEAD / 2), d = (idx % (HEAD / 2)) * 2;
-    float M = -INFINITY;
+  // Combines the four warps' states for (row r, dims d, d + 1): running maximum, denominator, numerators.
+  auto cta_reduce = [&](int r, int d, float& M, float& den, float& n0, float& n1) {
+    M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NW; ++w) M = fmaxf(M, mml[(w * 16 + r) * 2]);
-    float den = 0.f, n0 = 0.f, n1 = 0.f;
+    den = n0 = n1 = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const float wgt = exp2_approx(mml[(w * 16 + r) * 2] - M);  // 0 for warps that saw no token
+      const float mw = mml[(w * 16 + r) * 2];
+      const float wgt = mw == -INFINITY ? 0.f : exp2_approx(mw - M);  // warps that saw no token weigh nothing
       den += wgt * mml[(w * 16 + r) * 2 + 1];
       const float2 v = *reinterpret_cast<const float2*>(macc + (w * 16 + r) * C::ROW_F + d);
       n0 += wgt * v.x;
       n1 += wgt * v.y;
     }
-    const float inv = vscale / den;
-    const int head = head0 + r;
-    if (!partitioned) {
-      T* o = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head) * HEAD + d;
-      *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
-    } else {
-      const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.max_parts + part;
-      T* o = reinterpret_cast<T*>(p.tmp_out) + slot * HEAD + d;
-      *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
-      if (d == 0) {
-        p.max_logits[slot] = M;   // log2 domain
-        p.exp_sums[slot] = den;
+  };
+
+  if (csize == 1) {
+    for (int idx = threadIdx.x; idx < nrows * (HEAD / 2); idx += C::THREADS) {
+      const int r = idx / (HEAD / 2), d = (idx % (HEAD / 2)) * 2;
+      float M, den, n0, n1;
+      cta_reduce(r, d, M, den, n0, n1);
+      const float inv = vscale / den;
+      const int head = head0 + r;
+      if (!partitioned) {
+        T* o = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head) * HEAD + d;
+        *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
+      } else {
+        const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.max_parts + part;
+        T* o = reinterpret_cast<T*>(p.tmp_out) + slot * HEAD + d;
+        *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
+        if (d == 0) {
+          p.max_logits[slot] = M;   // log2 domain
+          p.exp_sums[slot] = den;
+        }
       }
     }
+    return;
   }
+
+  // ---- cluster mode: every CTA publishes its own (M, den, numerators) in shared memory, then rank 0
+  // combines the cluster's results through distributed shared memory and writes the output row.
+  cg::cluster_group cluster = cg::this_cluster();
+  float* cres = reinterpret_cast<float*>(smem + C::WARP_MERGE_BYTES);  // [16][ROW_F]
+  float* cml = cres + 16 * C::ROW_F;                                   // [16][2] = (M, den)
+  for (int idx = threadIdx.x; idx < nrows * (HEAD / 2); idx += C::THREADS) {
+    const int r = idx / (HEAD / 2), d = (idx % (HEAD / 2)) * 2;
+    float M, den, n0, n1;
+    cta_reduce(r, d, M, den, n0, n1);
+    *reinterpret_cast<float2*>(cres + r * C::ROW_F + d) = make_float2(n0, n1);
+    if (d == 0) {
+      cml[r * 2] = M;
+      cml[r * 2 + 1] = den;
+    }
+  }
+  cluster.sync();
+  if (cluster.block_rank() == 0) {
+    for (int idx = threadIdx.x; idx < nrows * (HEAD / 2); idx += C::THREADS) {
+      const int r = idx / (HEAD / 2), d = (idx % (HEAD / 2)) * 2;
+      float M = -INFINITY;
+      for (int c = 0; c < csize; ++c) M = fmaxf(M, cluster.map_shared_rank(cml, c)[r * 2]);
+      float den = 0.f, n0 = 0.f, n1 = 0.f;
+      for (int c = 0; c < csize; ++c) {
+        const float* rml = cluster.map_shared_rank(cml, c);
+        const float mc = rml[r * 2];
+        const float wgt = mc == -INFINITY ? 0.f : exp2_approx(mc - M);
+        den += wgt * rml[r * 2 + 1];
+        const float2 v = *reinterpret_cast<const float2*>(cluster.map_shared_rank(cres, c) + r * C::ROW_F + d);
+        n0 += wgt * v.x;
+        n1 += wgt * v.y;
+      }
+      const float inv = den > 0.f ? vscale / den : 0.f;  // empty context: zeros
+      T* o = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head0 + r) * HEAD + d;
+      *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
+    }
+  }
+  cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
 }
 
 // Merge of the partitions' results (the v2 reduce step; reference:
@@ -506,6 +695,8 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
                           const T* __restrict__ tmp_out, const uint32_t* __restrict__ context_lens, int max_parts,
                           int partition_size) {
   constexpr int NWARP = 4;
+  // Launched as a programmatic dependent of the partition kernel: wait until that grid's results are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, seq = blockIdx.y, num_heads = gridDim.x;
   const int ctx = static_cast<int>(context_lens[seq]);
   const int nparts = (ctx + partition_size - 1) / partition_size;

@@ -24,14 +24,45 @@ int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
   }
   const int gsplit = (p.group + 15) / 16;
   const bool partitioned = p.partition_size > 0;
-  dim3 grid(p.num_kv_heads * gsplit, p.num_seqs, partitioned ? p.max_parts : 1);
+  const int csize = partitioned ? 1 : (p.cluster < 1 ? 1 : p.cluster);
+  dim3 grid(p.num_kv_heads * gsplit, p.num_seqs, partitioned ? p.max_parts : csize);
+  if (csize > 1) {
+    // Single pass over a long context: a thread-block cluster splits it and merges through distributed
+    // shared memory, so no scratch buffer and no second launch are needed.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = csize;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) return PA_ERR_CUDA;
+    return PA_OK;
+  }
   kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p);
   if (partitioned) {
-    dim3 mgrid(p.num_heads, p.num_seqs);
-    const size_t msmem = (static_cast<size_t>(p.max_parts) + 4 * HEAD) * sizeof(float);
-    paged_decode_merge_kernel<T, HEAD><<<mgrid, 128, msmem, stream>>>(
-        reinterpret_cast<T*>(p.out), p.exp_sums, p.max_logits, reinterpret_cast<const T*>(p.tmp_out), p.context_lens,
-        p.max_parts, p.partition_size);
+    // The merge is launched as a programmatic dependent: it may be scheduled while the partition grid
+    // drains and waits (griddepcontrol.wait) until that grid's memory is visible.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.num_heads, p.num_seqs);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = (static_cast<size_t>(p.max_parts) + 4 * HEAD) * sizeof(float);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<T, HEAD>, reinterpret_cast<T*>(p.out),
+                           static_cast<const float*>(p.exp_sums), static_cast<const float*>(p.max_logits),
+                           reinterpret_cast<const T*>(p.tmp_out), p.context_lens, p.max_parts,
+                           p.partition_size) != cudaSuccess)
+      return PA_ERR_CUDA;
   }
   return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
 }
@@ -53,6 +84,10 @@ int launch_decode_mma_head(const DecodeParams& p, int block_size, cudaStream_t s
 // multiples of 32.
 template <typename T, bool FP8>
 int launch_decode_mma_impl(const DecodeParams& p, int head_size, int block_size, cudaStream_t stream) {
+#ifdef PA_ONLY_HEAD128  // tuning builds: one head size, to keep variant libraries small
+  if (head_size != 128) return PA_ERR_UNSUPPORTED;
+  return launch_decode_mma_head<T, FP8, 128>(p, block_size, stream);
+#else
   switch (head_size) {
     case 64: return launch_decode_mma_head<T, FP8, 64>(p, block_size, stream);
     case 96: return launch_decode_mma_head<T, FP8, 96>(p, block_size, stream);
@@ -67,6 +102,7 @@ int launch_decode_mma_impl(const DecodeParams& p, int head_size, int block_size,
       return PA_ERR_UNSUPPORTED;
     default: return PA_ERR_UNSUPPORTED;
   }
+#endif
 }
 
 }  // namespace pa

@@ -100,6 +100,19 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
   p.max_parts = a.partitioned ? (a.max_context_len + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE : 1;
   if (p.max_parts < 1) p.max_parts = 1;
   p.q_stride = a.q_stride;
+  // Single pass: how many CTAs (one thread-block cluster) share a (sequence, kv head) pair.  One CTA when
+  // the longest context is a single chunk; otherwise the smallest power of two, at most 8 and at most the
+  // number of chunks, that gives the GPU about four CTAs per SM (larger clusters schedule worse).
+  p.cluster = 1;
+  if (!a.partitioned) {
+    const int chunks = (a.max_context_len + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE;
+    const long pairs = static_cast<long>(a.num_seqs) * a.num_kv_heads * ((p.group + 15) / 16);
+    while (p.cluster < 8 && p.cluster * 2 <= chunks && pairs * p.cluster < 592) p.cluster *= 2;
+    if (const char* e = getenv("PA_V1_CLUSTER")) {   // tuning override
+      const int v = atoi(e);
+      if (v == 1 || v == 2 || v == 4 || v == 8) p.cluster = v;
+    }
+  }
   p.scale = a.scale;
   p.softcap = a.softcap;
   p.k_scale = a.k_scale;

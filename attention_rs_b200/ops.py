@@ -28,7 +28,8 @@ class _Tensor(ctypes.Structure):
 
 
 def library_path() -> str:
-    return os.path.join(_PKG_DIR, _LIB_NAME)
+    """Path of the shared library: next to this file, unless PA_B200_LIBRARY names another build."""
+    return os.environ.get("PA_B200_LIBRARY") or os.path.join(_PKG_DIR, _LIB_NAME)
 
 
 _lib: Optional[ctypes.CDLL] = None

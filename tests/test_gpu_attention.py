@@ -128,6 +128,22 @@ def test_generic_kernel_combinations(dev, combo, mode):
     check(run_ours(c, case_to_device(c, dev), mode), c.expected(), dtype, kv, what=f"generic {combo} {mode}")
 
 
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+def test_single_pass_cluster_sizes(dev, cluster, monkeypatch):
+    """The single-pass entry point splits long contexts over a thread-block cluster and merges through
+    distributed shared memory; every cluster size must give the same answer, including sequences with
+    fewer chunks than the cluster has CTAs and empty ones."""
+    monkeypatch.setenv("PA_V1_CLUSTER", str(cluster))
+    c = make_case([0, 1, 500, 513, 1100, 5000, 4096], 8, 2, 128, 16, "bf16", seed=81)
+    check(run_ours(c, case_to_device(c, dev), "v1"), c.expected(), "bf16", what=f"cluster {cluster}")
+    c = make_case([700, 3000, 40], 16, 2, 128, 16, "bf16", "fp8", seed=82)
+    check(run_ours(c, case_to_device(c, dev), "v1"), c.expected(), "bf16", "fp8", what=f"cluster {cluster} fp8")
+    c = make_case([2500, 9, 1025], 12, 1, 64, 32, "f16", seed=83, alibi=True, softcapping=20.0)
+    check(run_ours(c, case_to_device(c, dev), "v1"), c.expected(), "f16", what=f"cluster {cluster} alibi bs32")
+    c = make_case([1300, 600], 4, 2, 80, 8, "bf16", seed=84)
+    check(run_ours(c, case_to_device(c, dev), "v1"), c.expected(), "bf16", what=f"cluster {cluster} d80 bs8")
+
+
 def test_legacy_symbols_match_ex(dev):
     c = make_case([33, 700, 64], 8, 2, 128, 16, "bf16", seed=51)
     d = case_to_device(c, dev)
