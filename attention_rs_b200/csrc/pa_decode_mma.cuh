@@ -1,11 +1,11 @@
 // Paged decode attention for 16-bit queries on sm_100a.
 //
 // Work decomposition: one CTA per (sequence, kv head, context range).  All query
-// heads of the kv head's GQA group ride in the M dimension of warp-level
-// m16n8k16 MMAs, so each KV block is fetched from HBM once per group instead of
-// once per query head.  The reference launches one CTA per *query* head
-// (src/kernels/src/pagedattention.cu:147-150, grid at :632 and :806) and walks K
-// and V in two passes with dependent global loads (:200-246, :317-348).
+// heads of the kv head's GQA group share the CTA, so each KV block is fetched from
+// HBM once per group instead of once per query head.  The reference launches one
+// CTA per *query* head (src/kernels/src/pagedattention.cu:147-150, grid at :632 and
+// :806) and walks K and V in two passes with dependent global loads (:200-246,
+// :317-348).
 //
 // Data movement: for one (physical block, kv head) the K tile [HEAD/x][BS][x] and
 // the V tile [HEAD][BS] are each one contiguous run of HEAD*BS elements
@@ -16,20 +16,21 @@
 // each other inside the main loop; each keeps its own online-softmax state and
 // the CTA merges the per-warp states once at the end.
 //
-// Fragment mapping (the part that is easy to get wrong):
-//  * QK^T: A = Q (rows = query heads of the group, zero-padded to 16),
-//    B = K with n = token.  The two n-tiles of a 16-token tile hold the tokens
-//    {0,1,4,5,10,11,14,15} and {2,3,6,7,8,9,12,13}: every ldmatrix phase then
-//    touches 8 distinct 16-byte bank groups, and lane quad-index q ends up with
-//    the four logits of tokens 4q..4q+3.
-//  * PV: A = P straight from those registers, B = V with k = token.  Because lane
-//    q owns tokens 4q..4q+3 its B fragment is one 8-byte shared load from the V
-//    row (16-bit cache) or one 4-byte word (FP8 cache), conflict-free.
-//  * FP8 cache: the tiles feed m16n8k32 E4M3 MMAs directly (no per-element widening, which would
-//    make the kernel instruction-bound).  The other operand is split in two FP8 terms so that
-//    nothing is lost to its 3-bit mantissa: each query row is scaled to the E4M3 range and written
-//    as head + tail (two MMAs per tile), and so are the probabilities (scaled by 2^8).  The row
-//    scales, k_scale and v_scale are applied to the fp32 logits and the fp32 output.
+// Arithmetic: warp-level m16n8k16 MMAs in the "transposed" orientation, which
+// wastes no MMA rows on padding and keeps the accumulators small:
+//  * S^T = K Q^T: A = a 16-token tile of K straight from its cache layout (one
+//    ldmatrix.x4 per k-step), B = Q^T (8 heads per n-tile, resident in registers).
+//    The 16 MMA rows hold the tokens {0,1,4,5,10,11,14,15 | 2,3,6,7,8,9,12,13}:
+//    with that order every ldmatrix phase touches 8 distinct 16-byte bank groups.
+//  * softmax per head runs down the token rows (three shuffles per head).
+//  * O^T = V^T P^T: A = V^T, again straight from the cache layout: lane quad-index
+//    q owns tokens 4q..4q+3, so its fragment is one 8-byte shared load per row
+//    (16-bit cache) or one ldmatrix word (FP8 cache), conflict-free.  B = P^T comes
+//    from the S^T accumulators through movmatrix (an 8x8 transpose across the warp).
+//  * FP8 cache: bytes are widened to f16 with cvt.e4m3x2 on the way into the MMA
+//    and the query is converted to f16 once; k_scale multiplies the fp32 logits and
+//    v_scale the fp32 output.  (Feeding the bytes to E4M3 MMAs directly was tried
+//    and is slower on this part.)
 #pragma once
 
 #include <cooperative_groups.h>
@@ -58,19 +59,24 @@ struct DecodeParams {
   int max_num_blocks_per_seq, max_parts, q_stride;
   int partition_size;         // 0: the CTA (or cluster) covers the whole context
   int cluster;                // single pass only: CTAs per (sequence, kv head) that split the context (1 = one CTA)
+  int parts_per_cta;          // partitioned only: consecutive partitions one CTA walks (their merged result goes to the
+                              // first one's scratch slot, the others are marked empty)
   float scale, softcap, k_scale, v_scale;
 };
 
-template <typename T, bool FP8, int HEAD, int BS>
-struct DecodeCfg {
-  using MT = T;  // input type of the 16-bit MMAs (the FP8 path uses E4M3 MMAs instead)
-  static constexpr int ES = FP8 ? 1 : 2;
 #ifndef PA_STAGE_TOKENS_16BIT
 #define PA_STAGE_TOKENS_16BIT 16
 #endif
 #ifndef PA_STAGE_TOKENS_FP8
 #define PA_STAGE_TOKENS_FP8 32
 #endif
+
+// NH: n-tiles of 8 query heads handled by one CTA (1: groups up to 8, 2: up to 16; larger groups take
+// several CTAs per kv head).
+template <typename T, bool FP8, int HEAD, int BS, int NH>
+struct DecodeCfg {
+  using MT = std::conditional_t<FP8, __half, T>;  // MMA input type
+  static constexpr int ES = FP8 ? 1 : 2;
   // Tokens per stage: at least one physical block and one 16-token MMA tile.  An FP8 stage takes 32
   // tokens so that it carries as many bytes, and as much independent work per warp, as a 16-bit one.
   static constexpr int STOK_MIN = FP8 ? PA_STAGE_TOKENS_FP8 : PA_STAGE_TOKENS_16BIT;
@@ -79,38 +85,40 @@ struct DecodeCfg {
   static constexpr int TT = STOK / 16;               // 16-token tiles per stage
   static constexpr int TILE_BYTES = HEAD * BS * ES;  // one block's K tile (V tile is the same size)
   static constexpr int STAGE_BYTES = 2 * SB * TILE_BYTES;
+  // Warps and ring depth: about 64 KB of ring per CTA, i.e. three CTAs per SM at the common tile sizes;
+  // that measured faster than fewer CTAs with deeper rings or more warps.
 #ifdef PA_FORCE_NW
   static constexpr int NW = PA_FORCE_NW;
 #else
-  static constexpr int NW = STAGE_BYTES <= 12 * 1024 ? 4 : (STAGE_BYTES <= 16 * 1024 ? 3 : 2);
+  static constexpr int NW = STAGE_BYTES <= 8 * 1024 ? 4 : (STAGE_BYTES <= 12 * 1024 ? 3 : 2);
 #endif
 #ifdef PA_FORCE_STAGES
   static constexpr int STAGES = PA_FORCE_STAGES;
 #else
-  static constexpr int STAGES_RAW = (104 * 1024) / (NW * STAGE_BYTES);
-  static constexpr int STAGES = STAGES_RAW < 2 ? 2 : (STAGES_RAW > 4 ? 4 : STAGES_RAW);
+  static constexpr int STAGES = STAGE_BYTES <= 4 * 1024 ? 4 : 2;
 #endif
   static constexpr int THREADS = NW * WARP;
   static constexpr int RING_BYTES = NW * STAGES * STAGE_BYTES;
-  static constexpr int ROW_F = HEAD + 8;  // padded fp32 row of the merge buffer
+  static constexpr int ROW_F = HEAD + 4;  // padded fp32 row of the merge buffers (keeps their stores conflict-free)
   static constexpr int WARP_MERGE_BYTES = NW * 16 * ROW_F * 4 + NW * 16 * 2 * 4;  // per-warp (acc, m, l)
   static constexpr int MERGE_BYTES = WARP_MERGE_BYTES + 16 * ROW_F * 4 + 16 * 2 * 4;  // + the CTA's own result (cluster mode)
   static constexpr int DATA_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
   static constexpr int BAR_BYTES = NW * STAGES * 2 * 8;
   static constexpr int SMEM_BYTES = DATA_BYTES + BAR_BYTES + 128;  // +128: manual alignment slack
   static_assert(HEAD % 16 == 0, "head size must be a multiple of 16");
+  static_assert(NH == 1 || NH == 2, "one or two n-tiles of heads");
   static_assert(!FP8 || (HEAD % 32 == 0 && BS >= 16), "FP8 path needs HEAD % 32 == 0 and block_size >= 16");
 };
 
-template <typename T, bool FP8, int HEAD, int BS>
-__global__ void __launch_bounds__(DecodeCfg<T, FP8, HEAD, BS>::THREADS)
+template <typename T, bool FP8, int HEAD, int BS, int NH>
+__global__ void __launch_bounds__(DecodeCfg<T, FP8, HEAD, BS, NH>::THREADS)
 paged_decode_mma_kernel(const DecodeParams p) {
-  using C = DecodeCfg<T, FP8, HEAD, BS>;
+  using C = DecodeCfg<T, FP8, HEAD, BS, NH>;
   using MT = typename C::MT;
   constexpr int NW = C::NW, STAGES = C::STAGES, SB = C::SB, STOK = C::STOK, TT = C::TT;
   constexpr int TILE_BYTES = C::TILE_BYTES, STAGE_BYTES = C::STAGE_BYTES;
-  constexpr int KSTEPS = FP8 ? HEAD / 32 : HEAD / 16;  // MMA k-steps of QK^T
-  constexpr int NT = HEAD / 8;       // n-tiles of PV
+  constexpr int KSTEPS = HEAD / 16;  // MMA k-steps of S^T = K Q^T
+  constexpr int DT = HEAD / 16;      // 16-row tiles of O^T = V^T P^T
 
   namespace cg = cooperative_groups;
   constexpr int PART = PA_PARTITION_SIZE;   // the context is walked in chunks of this many tokens
@@ -122,19 +130,20 @@ paged_decode_mma_kernel(const DecodeParams p) {
 
   const int seq = blockIdx.y;
   const int ctx = static_cast<int>(p.context_lens[seq]);
-  const int gsplit = (p.group + 15) / 16;               // head sub-groups per kv head (1 unless group > 16)
+  constexpr int HPC = 8 * NH;                            // query heads per CTA
+  const int gsplit = (p.group + HPC - 1) / HPC;          // CTAs per kv head (1 unless the group is larger than HPC)
   const int kvh = blockIdx.x / gsplit;
-  const int head0 = kvh * p.group + (blockIdx.x % gsplit) * 16;
-  const int nrows = min(16, kvh * p.group + p.group - head0);  // live rows of the M tile
-  const bool rows16 = nrows > 8;
+  const int head0 = kvh * p.group + (blockIdx.x % gsplit) * HPC;
+  const int nrows = min(HPC, kvh * p.group + p.group - head0);  // live heads of this CTA
   const bool partitioned = p.partition_size > 0;
   const int csize = partitioned ? 1 : p.cluster;        // CTAs sharing this (sequence, kv head)
   const int part = blockIdx.z;                          // partition (v2) or rank in the cluster (v1)
 
-  // Chunks of PART tokens owned by this CTA: first, first + cstride, ...  (v2: exactly one.)
-  const int first = (partitioned || csize > 1) ? part : 0;
-  const int cstride = partitioned ? (1 << 20) : csize;
-  const int t_end = partitioned ? min(ctx, (first + 1) * PART) : ctx;
+  // Chunks of PART tokens owned by this CTA: first, first + cstride, ...  Partitioned: parts_per_cta
+  // consecutive partitions.  Single pass: every csize-th chunk of the whole context.
+  const int first = partitioned ? part * p.parts_per_cta : (csize > 1 ? part : 0);
+  const int cstride = partitioned ? 1 : csize;
+  const int t_end = partitioned ? min(ctx, (first + p.parts_per_cta) * PART) : ctx;
   const int nchunks_total = (t_end + PART - 1) / PART;
   const int my_chunks = first < nchunks_total ? (nchunks_total - 1 - first) / cstride + 1 : 0;
   if (csize == 1 && my_chunks == 0 && partitioned) return;  // nothing to do for this partition
@@ -230,133 +239,88 @@ paged_decode_mma_kernel(const DecodeParams p) {
   for (int i = 0; i < STAGES; ++i)
     if (i < n_mine) issue(i);
 
-  // ---- query fragments (A operand), zero rows beyond the group
-  // 16-bit path: qa[j] = the four A registers of k-step j.  FP8 path: qa = head terms, qb = tail terms,
-  // and qinv_* undo the per-row scaling that brought the row into the E4M3 range.
-  uint32_t qa[KSTEPS][4];
-  uint32_t qb[FP8 ? KSTEPS : 1][4];
-  float qinv_lo = 1.f, qinv_hi = 1.f;
+  // ---- query fragments (B operand of S^T = K Q^T): lane (g, q) holds head nh*8 + g, two dim pairs per k-step
+  uint32_t qb[KSTEPS][NH][2];
   {
     const T* qbase = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(seq) * p.q_stride + static_cast<int64_t>(head0) * HEAD;
-    if constexpr (!FP8) {
-      auto ldq = [&](int row, int col) -> uint32_t {  // two consecutive elements
-        return row < nrows ? *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col) : 0u;
-      };
-#pragma unroll
-      for (int j = 0; j < KSTEPS; ++j) {
-        qa[j][0] = ldq(gi, 16 * j + 2 * qi);
-        qa[j][1] = ldq(gi + 8, 16 * j + 2 * qi);
-        qa[j][2] = ldq(gi, 16 * j + 8 + 2 * qi);
-        qa[j][3] = ldq(gi + 8, 16 * j + 8 + 2 * qi);
+    auto ldq = [&](int row, int col) -> uint32_t {  // two consecutive elements as an MT pair; zero beyond the group
+      if (row >= nrows) return 0u;
+      const uint32_t raw = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col);
+      if constexpr (std::is_same<T, MT>::value) {
+        return raw;
+      } else {  // bf16 query, f16 MMA (FP8 cache)
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+        return pack2<__half>(f.x, f.y);
       }
-      (void)qb;
-    } else {
-      // This lane's 4-element runs of rows gi and gi + 8: dims 32j + 4q.. and 32j + 16 + 4q..
-      // Two passes over the (tiny, cached) query rows keep the register footprint small: the first finds
-      // each row's largest magnitude, the second scales and splits.
-      auto load4 = [&](int j, int reg, float (&v)[4]) {
-        const int row = gi + (reg & 1) * 8, col = 32 * j + (reg >> 1) * 16 + 4 * qi;
-        uint2 raw = make_uint2(0u, 0u);
-        if (row < nrows) {
-          raw.x = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col);
-          raw.y = *reinterpret_cast<const uint32_t*>(qbase + row * HEAD + col + 2);
-        }
-        const T* e = reinterpret_cast<const T*>(&raw);
+    };
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = to_f32<T>(e[k]);
-      };
-      float amax_lo = 0.f, amax_hi = 0.f;
+    for (int j = 0; j < KSTEPS; ++j) {
 #pragma unroll
-      for (int j = 0; j < KSTEPS; ++j) {
-#pragma unroll
-        for (int reg = 0; reg < 4; ++reg) {
-          float v[4];
-          load4(j, reg, v);
-          const float m4 = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-          if (reg & 1) amax_hi = fmaxf(amax_hi, m4);
-          else amax_lo = fmaxf(amax_lo, m4);
-        }
-      }
-      amax_lo = fmaxf(amax_lo, __shfl_xor_sync(0xffffffffu, amax_lo, 1));
-      amax_lo = fmaxf(amax_lo, __shfl_xor_sync(0xffffffffu, amax_lo, 2));
-      amax_hi = fmaxf(amax_hi, __shfl_xor_sync(0xffffffffu, amax_hi, 1));
-      amax_hi = fmaxf(amax_hi, __shfl_xor_sync(0xffffffffu, amax_hi, 2));
-      // Scale the row so that its largest element sits at 224 (half the E4M3 maximum).
-      const float qs_lo = amax_lo > 0.f && amax_lo < 3.0e38f ? 224.f / amax_lo : 1.f;
-      const float qs_hi = amax_hi > 0.f && amax_hi < 3.0e38f ? 224.f / amax_hi : 1.f;
-      qinv_lo = 1.f / qs_lo;
-      qinv_hi = 1.f / qs_hi;
-#pragma unroll
-      for (int j = 0; j < KSTEPS; ++j) {
-#pragma unroll
-        for (int reg = 0; reg < 4; ++reg) {
-          float v[4];
-          load4(j, reg, v);
-          const float sc = (reg & 1) ? qs_hi : qs_lo;
-          uint32_t h01, t01, h23, t23;
-          split_e4m3x2(v[0] * sc, v[1] * sc, h01, t01);
-          split_e4m3x2(v[2] * sc, v[3] * sc, h23, t23);
-          qa[j][reg] = h01 | (h23 << 16);
-          qb[j][reg] = t01 | (t23 << 16);
+      for (int nh = 0; nh < NH; ++nh) {
+        if constexpr (!FP8) {
+          qb[j][nh][0] = ldq(nh * 8 + gi, 16 * j + 2 * qi);
+          qb[j][nh][1] = ldq(nh * 8 + gi, 16 * j + 8 + 2 * qi);
+        } else {  // k-slot order of the FP8 chunks: lane q owns bytes 4q..4q+3 of each 16-byte chunk
+          qb[j][nh][0] = ldq(nh * 8 + gi, 16 * j + 4 * qi);
+          qb[j][nh][1] = ldq(nh * 8 + gi, 16 * j + 4 * qi + 2);
         }
       }
     }
   }
 
   // ---- per-lane shared-memory offsets
-  // K (ldmatrix row addresses).  Matrix mi = lane / 8, row r = lane % 8.
+  // Token (0..15, within a 16-token tile) held by MMA row r of row-set `set` (0: rows 0-7, 1: rows 8-15).
+  auto tile_token = [](int set, int r) { return 4 * (r >> 1) + (r & 1) + ((((r >> 2) ^ set) & 1) ? 2 : 0); };
+  // K (ldmatrix row addresses).  Matrix mi = lane / 8 feeds row-set mi % 2 with 16-byte chunk mi / 2.
   uint32_t koff[TT];
   {
     const int mi = lane >> 3, r = lane & 7;
-    const int tile = mi >> 1;     // which n-tile this matrix feeds
-    const int chunk = mi & 1;     // which 16-byte chunk of the k-step
-    const int tau = 4 * (r >> 1) + (r & 1) + ((((r >> 2) ^ tile) & 1) ? 2 : 0);
+    const int tau = tile_token(mi & 1, r);
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
       const int ts = tt * 16 + tau;
-      koff[tt] = (ts / BS) * TILE_BYTES + (chunk * BS + (ts % BS)) * 16;
+      koff[tt] = (ts / BS) * TILE_BYTES + ((mi >> 1) * BS + (ts % BS)) * 16;
     }
   }
-  // V.  16-bit: one 8-byte load per n-tile at row gi.  FP8: ldmatrix rows; one x4 load brings, for two
-  // n-tiles, the 16-byte halves that hold stage tokens 0-15 and 16-31 (voff8: matrix mi = lane / 8 serves
-  // n-tile mi / 2, half mi % 2).
+  // V.  16-bit: 8-byte loads at rows (dims) gi and gi + 8: tokens 4q..4q+3.  FP8: ldmatrix rows, matrix mi
+  // covering dims mi*8..mi*8+7.
   uint32_t voff[TT];
-  uint32_t voff8 = 0;
-  if constexpr (FP8) {
-    static_assert(!FP8 || TT == 2, "the FP8 path walks 32-token stages");
-    const int mi = lane >> 3, r = lane & 7, half = mi & 1;
-    const int vb = (half * 16) / BS, vo = (half * 16) % BS;
-    voff8 = (SB + vb) * TILE_BYTES + ((mi >> 1) * 8 + r) * BS + vo;
-  }
 #pragma unroll
   for (int tt = 0; tt < TT; ++tt) {
     const int vb = (tt * 16) / BS, vo = (tt * 16) % BS;  // block within the stage and token offset in it
     if constexpr (FP8) {
-      voff[tt] = 0;
+      voff[tt] = (SB + vb) * TILE_BYTES + (lane * BS) + vo;       // lane = mi * 8 + r = dim within 32
     } else if constexpr (BS >= 16) {
       voff[tt] = (SB + vb) * TILE_BYTES + (gi * BS + vo + 4 * qi) * 2;
     } else {
       voff[tt] = (SB + 2 * tt + (qi >> 1)) * TILE_BYTES + (gi * BS + (qi & 1) * 4) * 2;
     }
   }
-  // Tokens (within a 16-token tile) behind this lane's logits: n-tile 0 -> tokA, tokA+1; n-tile 1 -> tokB, tokB+1.
-  const int tokA = 4 * qi + ((qi & 2) ? 2 : 0);
-  const int tokB = 4 * qi + ((qi & 2) ? 0 : 2);
+  // Tokens (within a tile) of this lane's two S^T rows.
+  const int tok_lo = tile_token(0, gi), tok_hi = tile_token(1, gi);
 
-  // ---- softmax state (log2 domain) and output accumulators
+  // ---- softmax state (log2 domain; one per head this lane sees: heads nh*8 + 2q, + 1) and accumulators
   const bool plain = (p.softcap == 1.0f) && (p.alibi_slopes == nullptr);
   const float kscale = FP8 ? p.k_scale : 1.0f;
   const float qk_scale = p.scale * kscale;
   const float qk_scale_log2 = qk_scale * LOG2E;
-  float slope_lo = 0.f, slope_hi = 0.f;
-  if (p.alibi_slopes != nullptr) {
-    if (gi < nrows) slope_lo = p.alibi_slopes[head0 + gi];
-    if (gi + 8 < nrows) slope_hi = p.alibi_slopes[head0 + gi + 8];
-  }
-  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-  float acc[NT][4];
+  float slope[NH][2];
+  float m_run[NH][2], l_run[NH][2];
 #pragma unroll
-  for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  for (int nh = 0; nh < NH; ++nh) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = nh * 8 + 2 * qi + e;
+      slope[nh][e] = (p.alibi_slopes != nullptr && h < nrows) ? p.alibi_slopes[head0 + h] : 0.f;
+      m_run[nh][e] = -INFINITY;
+      l_run[nh][e] = 0.f;
+    }
+  }
+  float acc[DT][NH][4];  // O^T: [dim tile][head tile]{(dim g, head 2q), (g, 2q+1), (g+8, 2q), (g+8, 2q+1)}
+#pragma unroll
+  for (int d = 0; d < DT; ++d)
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) acc[d][nh][0] = acc[d][nh][1] = acc[d][nh][2] = acc[d][nh][3] = 0.f;
 
   bool healthy = true;
   int ck = 0, cj = 0;  // chunk ordinal and stage-within-chunk of local stage i
@@ -389,150 +353,131 @@ paged_decode_mma_kernel(const DecodeParams p) {
     if (i + STAGES < n_mine) issue(i + STAGES);
     continue;
 #endif
-    // ---------------- logits of the stage's tiles (independent MMA chains: they overlap)
-    float sc[TT][2][4];
+    // ---------------- S^T of the stage's tiles (independent MMA chains: they overlap)
+    float sc[TT][NH][4];
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) {
+    for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
-      for (int h = 0; h < 2; ++h) sc[tt][h][0] = sc[tt][h][1] = sc[tt][h][2] = sc[tt][h][3] = 0.f;
-    }
+      for (int nh = 0; nh < NH; ++nh) sc[tt][nh][0] = sc[tt][nh][1] = sc[tt][nh][2] = sc[tt][nh][3] = 0.f;
     if constexpr (!FP8) {
 #pragma unroll
       for (int j = 0; j < KSTEPS; ++j) {
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
           if (TT == 1 || stage_tok0 + tt * 16 < t_end) {
-            uint32_t r0, r1, r2, r3;
-            ldmatrix_x4(stage + koff[tt] + j * (2 * BS * 16), r0, r1, r2, r3);
-            mma16816<MT>(sc[tt][0], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r0, r1);
-            mma16816<MT>(sc[tt][1], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r2, r3);
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(stage + koff[tt] + j * (2 * BS * 16), a0, a1, a2, a3);
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) mma16816<MT>(sc[tt][nh], a0, a1, a2, a3, qb[j][nh][0], qb[j][nh][1]);
           }
         }
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < KSTEPS; ++j) {
+      for (int j = 0; j < KSTEPS; j += 2) {
 #pragma unroll
         for (int tt = 0; tt < TT; ++tt) {
-          if (stage_tok0 + tt * 16 < t_end) {
-            uint32_t r0, r1, r2, r3;
-            ldmatrix_x4(stage + koff[tt] + j * (2 * BS * 16), r0, r1, r2, r3);
-            mma16832_e4m3(sc[tt][0], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r0, r1);
-            mma16832_e4m3(sc[tt][1], qa[j][0], qa[j][1], qa[j][2], qa[j][3], r2, r3);
-            mma16832_e4m3(sc[tt][0], qb[j][0], qb[j][1], qb[j][2], qb[j][3], r0, r1);
-            mma16832_e4m3(sc[tt][1], qb[j][0], qb[j][1], qb[j][2], qb[j][3], r2, r3);
+          if (TT == 1 || stage_tok0 + tt * 16 < t_end) {
+            uint32_t r0, r1, r2, r3;  // (rows 0-7, chunk j), (rows 8-15, chunk j), (rows 0-7, chunk j+1), (rows 8-15, chunk j+1)
+            ldmatrix_x4(stage + koff[tt] + (j / 2) * (2 * BS * 16), r0, r1, r2, r3);
+            const uint32_t a0 = e4m3x2_to_f16x2(r0), a2 = e4m3x2_to_f16x2(r0 >> 16);
+            const uint32_t a1 = e4m3x2_to_f16x2(r1), a3 = e4m3x2_to_f16x2(r1 >> 16);
+            const uint32_t c0 = e4m3x2_to_f16x2(r2), c2 = e4m3x2_to_f16x2(r2 >> 16);
+            const uint32_t c1 = e4m3x2_to_f16x2(r3), c3 = e4m3x2_to_f16x2(r3 >> 16);
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) {
+              mma16816<MT>(sc[tt][nh], a0, a1, a2, a3, qb[j][nh][0], qb[j][nh][1]);
+              mma16816<MT>(sc[tt][nh], c0, c1, c2, c3, qb[j + 1][nh][0], qb[j + 1][nh][1]);
+            }
           }
         }
       }
     }
 
-    // ---------------- online softmax over the whole stage (one max / one rescale per stage)
-    // x[tt][0..3]: logits (log2 domain) of tokens tokA, tokA+1, tokB, tokB+1 of tile tt; -inf when masked.
-    auto logits_of = [&](int rowsel, float slope, float rowscale, float (&x)[TT][4]) {
+    // ---------------- online softmax over the whole stage (one max / one rescale per stage and head)
+    // sc[tt][nh] = {S(tok_lo, head 2q), S(tok_lo, 2q+1), S(tok_hi, 2q), S(tok_hi, 2q+1)}; logits in the log2 domain.
+    bool grow = false;
+    float m_new[NH][2];
+#pragma unroll
+    for (int nh = 0; nh < NH; ++nh) {
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int tt = 0; tt < TT; ++tt) {
-        const int ta = stage_tok0 + tt * 16 + tokA, tb = stage_tok0 + tt * 16 + tokB;
-        float x0 = sc[tt][0][rowsel], x1 = sc[tt][0][rowsel + 1], x2 = sc[tt][1][rowsel], x3 = sc[tt][1][rowsel + 1];
+        const int ta = stage_tok0 + tt * 16 + tok_lo, tb = stage_tok0 + tt * 16 + tok_hi;
+        float x0 = sc[tt][nh][0], x1 = sc[tt][nh][1], x2 = sc[tt][nh][2], x3 = sc[tt][nh][3];
         if (plain) {
-          const float f = qk_scale_log2 * rowscale;
-          x0 *= f; x1 *= f; x2 *= f; x3 *= f;
+          x0 *= qk_scale_log2; x1 *= qk_scale_log2; x2 *= qk_scale_log2; x3 *= qk_scale_log2;
         } else {
-          const float f = qk_scale * rowscale;
-          x0 *= f; x1 *= f; x2 *= f; x3 *= f;
+          x0 *= qk_scale; x1 *= qk_scale; x2 *= qk_scale; x3 *= qk_scale;
           if (p.softcap != 1.0f) {
             const float inv = 1.0f / p.softcap;
             x0 = tanh_approx(x0 * inv) * p.softcap; x1 = tanh_approx(x1 * inv) * p.softcap;
             x2 = tanh_approx(x2 * inv) * p.softcap; x3 = tanh_approx(x3 * inv) * p.softcap;
           }
-          x0 = (x0 + slope * static_cast<float>(ta - ctx + 1)) * LOG2E;
-          x1 = (x1 + slope * static_cast<float>(ta + 1 - ctx + 1)) * LOG2E;
-          x2 = (x2 + slope * static_cast<float>(tb - ctx + 1)) * LOG2E;
-          x3 = (x3 + slope * static_cast<float>(tb + 1 - ctx + 1)) * LOG2E;
+          const float da = static_cast<float>(ta - ctx + 1), db = static_cast<float>(tb - ctx + 1);
+          x0 = (x0 + slope[nh][0] * da) * LOG2E;
+          x1 = (x1 + slope[nh][1] * da) * LOG2E;
+          x2 = (x2 + slope[nh][0] * db) * LOG2E;
+          x3 = (x3 + slope[nh][1] * db) * LOG2E;
         }
-        x[tt][0] = ta < t_end ? x0 : -INFINITY;
-        x[tt][1] = ta + 1 < t_end ? x1 : -INFINITY;
-        x[tt][2] = tb < t_end ? x2 : -INFINITY;
-        x[tt][3] = tb + 1 < t_end ? x3 : -INFINITY;
+        const bool va = ta < t_end, vb = tb < t_end;
+        sc[tt][nh][0] = x0 = va ? x0 : -INFINITY;
+        sc[tt][nh][1] = x1 = va ? x1 : -INFINITY;
+        sc[tt][nh][2] = x2 = vb ? x2 : -INFINITY;
+        sc[tt][nh][3] = x3 = vb ? x3 : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(x0, x2));
+        mx1 = fmaxf(mx1, fmaxf(x1, x3));
       }
-    };
-    auto row_max = [&](const float (&x)[TT][4]) {
-      float mx = -INFINITY;
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) mx = fmaxf(mx, fmaxf(fmaxf(x[tt][0], x[tt][1]), fmaxf(x[tt][2], x[tt][3])));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      return fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    };
-    // P fragments.  16-bit path: pa_*[tile][k-lo / k-hi]; lane q pairs tokens (4q, 4q+1) with V's low word and
-    // (4q+2, 4q+3) with its high word.  FP8 path: pa_*[tile][head / tail], each register the four bytes of
-    // tokens 4q..4q+3; probabilities carry a factor 2^8 (kPBias) that cancels between numerator and denominator.
-    constexpr float kPBias = FP8 ? 8.f : 0.f;
-    uint32_t pa_lo[TT][2], pa_hi[TT][2];
-    auto probs = [&](const float (&x)[TT][4], float m, float& l, uint32_t (&pa)[TT][2]) {
-      float sum = 0.f;
-      const float mb = m - kPBias;
-#pragma unroll
-      for (int tt = 0; tt < TT; ++tt) {
-        const float p0 = exp2_approx(x[tt][0] - mb), p1 = exp2_approx(x[tt][1] - mb);
-        const float p2 = exp2_approx(x[tt][2] - mb), p3 = exp2_approx(x[tt][3] - mb);
-        sum += (p0 + p1) + (p2 + p3);
-        if constexpr (!FP8) {
-          const uint32_t pA = pack2<MT>(p0, p1), pB = pack2<MT>(p2, p3);
-          pa[tt][0] = (qi & 2) ? pB : pA;
-          pa[tt][1] = (qi & 2) ? pA : pB;
-        } else {
-          uint32_t hA, tA, hB, tB;
-          split_e4m3x2(p0, p1, hA, tA);   // tokens tokA, tokA + 1
-          split_e4m3x2(p2, p3, hB, tB);   // tokens tokB, tokB + 1
-          pa[tt][0] = (qi & 2) ? (hB | (hA << 16)) : (hA | (hB << 16));
-          pa[tt][1] = (qi & 2) ? (tB | (tA << 16)) : (tA | (tB << 16));
-        }
+      for (int o = 4; o <= 16; o <<= 1) {   // down the token rows: lanes that share q
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
       }
-      l += sum;
-    };
-    float x_lo[TT][4], x_hi[TT][4];
-    logits_of(0, slope_lo, qinv_lo, x_lo);
-    float mn_lo = fmaxf(m_lo, row_max(x_lo)), mn_hi = m_hi;   // finite: the stage's first token is valid
-    if (rows16) {
-      logits_of(2, slope_hi, qinv_hi, x_hi);
-      mn_hi = fmaxf(m_hi, row_max(x_hi));
+      m_new[nh][0] = fmaxf(m_run[nh][0], mx0);   // finite: the stage's first token is valid
+      m_new[nh][1] = fmaxf(m_run[nh][1], mx1);
+      grow = grow || m_new[nh][0] > m_run[nh][0] || m_new[nh][1] > m_run[nh][1];
     }
-    // Rescale what earlier stages accumulated only when some row's running maximum moved.
-    if (__any_sync(0xffffffffu, mn_lo > m_lo || mn_hi > m_hi)) {
-      const float corr_lo = exp2_approx(m_lo - mn_lo);
-      l_lo *= corr_lo;
+    // Rescale what earlier stages accumulated only when some head's running maximum moved.
+    if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        acc[n][0] *= corr_lo;
-        acc[n][1] *= corr_lo;
-      }
-      if (rows16) {
-        const float corr_hi = exp2_approx(m_hi - mn_hi);
-        l_hi *= corr_hi;
+      for (int nh = 0; nh < NH; ++nh) {
+        const float c0 = exp2_approx(m_run[nh][0] - m_new[nh][0]), c1 = exp2_approx(m_run[nh][1] - m_new[nh][1]);
+        l_run[nh][0] *= c0;
+        l_run[nh][1] *= c1;
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          acc[n][2] *= corr_hi;
-          acc[n][3] *= corr_hi;
+        for (int d = 0; d < DT; ++d) {
+          acc[d][nh][0] *= c0; acc[d][nh][1] *= c1; acc[d][nh][2] *= c0; acc[d][nh][3] *= c1;
         }
+        m_run[nh][0] = m_new[nh][0];
+        m_run[nh][1] = m_new[nh][1];
       }
-      m_lo = mn_lo;
-      m_hi = mn_hi;
     }
-    probs(x_lo, m_lo, l_lo, pa_lo);
-    if (rows16) {
-      probs(x_hi, m_hi, l_hi, pa_hi);
-    } else {
+    // Probabilities, then P^T as B fragments: movmatrix turns (token row g, heads 2q, 2q+1) into
+    // (head g, tokens of rows 2q, 2q+1).  Lane q then pairs tokens (4q, 4q+1) with V's low word and
+    // (4q+2, 4q+3) with its high word; for q >= 2 the two row-sets hold them the other way round.
+    uint32_t pb[TT][NH][2];
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) pa_hi[tt][0] = pa_hi[tt][1] = 0u;
+    for (int tt = 0; tt < TT; ++tt) {
+#pragma unroll
+      for (int nh = 0; nh < NH; ++nh) {
+        const float p0 = exp2_approx(sc[tt][nh][0] - m_run[nh][0]), p1 = exp2_approx(sc[tt][nh][1] - m_run[nh][1]);
+        const float p2 = exp2_approx(sc[tt][nh][2] - m_run[nh][0]), p3 = exp2_approx(sc[tt][nh][3] - m_run[nh][1]);
+        l_run[nh][0] += p0 + p2;
+        l_run[nh][1] += p1 + p3;
+        const uint32_t tA = movmatrix_trans(pack2<MT>(p0, p1)), tB = movmatrix_trans(pack2<MT>(p2, p3));
+        pb[tt][nh][0] = (qi & 2) ? tB : tA;
+        pb[tt][nh][1] = (qi & 2) ? tA : tB;
+      }
     }
 
-    // ---------------- PV
+    // ---------------- O^T += V^T P^T
     healthy = __all_sync(0xffffffffu, mbar_wait(bv, par, p.status));
     if (!healthy) break;
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
       const int tile_tok0 = stage_tok0 + tt * 16;
       if (TT == 1 || tile_tok0 < t_end) {
-        // Cache memory past the context may hold anything (NaNs included): clear those V words.
+        // Cache memory past the context may hold anything (NaNs included): clear those V elements.
         const bool partial = tile_tok0 + 16 > t_end;
         const int vt = tile_tok0 + 4 * qi;  // first of this lane's four tokens
         if constexpr (!FP8) {
@@ -542,36 +487,36 @@ paged_decode_mma_kernel(const DecodeParams p) {
             mk1 = (vt + 2 < t_end ? 0x0000ffffu : 0u) | (vt + 3 < t_end ? 0xffff0000u : 0u);
           }
 #pragma unroll
-          for (int n = 0; n < NT; ++n) {
-            uint32_t b0, b1;
-            lds64(stage + voff[tt] + n * (8 * BS * 2), b0, b1);
-            if (partial) { b0 &= mk0; b1 &= mk1; }
-            mma16816<MT>(acc[n], pa_lo[tt][0], pa_hi[tt][0], pa_lo[tt][1], pa_hi[tt][1], b0, b1);
+          for (int d = 0; d < DT; ++d) {
+            uint32_t a0, a1, a2, a3;  // (dim g, tokens 4q,4q+1), (dim g+8, same), (dim g, 4q+2,4q+3), (dim g+8, same)
+            lds64(stage + voff[tt] + d * (16 * BS * 2), a0, a2);
+            lds64(stage + voff[tt] + d * (16 * BS * 2) + 8 * BS * 2, a1, a3);
+            if (partial) { a0 &= mk0; a1 &= mk0; a2 &= mk1; a3 &= mk1; }
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) mma16816<MT>(acc[d][nh], a0, a1, a2, a3, pb[tt][nh][0], pb[tt][nh][1]);
+          }
+        } else {
+          uint32_t mk = 0xffffffffu;
+          if (partial) {
+            mk = (vt < t_end ? 0x000000ffu : 0u) | (vt + 1 < t_end ? 0x0000ff00u : 0u) |
+                 (vt + 2 < t_end ? 0x00ff0000u : 0u) | (vt + 3 < t_end ? 0xff000000u : 0u);
+          }
+#pragma unroll
+          for (int d = 0; d < DT; d += 2) {
+            uint32_t r0, r1, r2, r3;  // words of dims d*16 + g, + 8, + 16, + 24: tokens 4q..4q+3
+            ldmatrix_x4(stage + voff[tt] + (d / 2) * (32 * BS), r0, r1, r2, r3);
+            if (partial) { r0 &= mk; r1 &= mk; r2 &= mk; r3 &= mk; }
+            const uint32_t a0 = e4m3x2_to_f16x2(r0), a2 = e4m3x2_to_f16x2(r0 >> 16);
+            const uint32_t a1 = e4m3x2_to_f16x2(r1), a3 = e4m3x2_to_f16x2(r1 >> 16);
+            const uint32_t c0 = e4m3x2_to_f16x2(r2), c2 = e4m3x2_to_f16x2(r2 >> 16);
+            const uint32_t c1 = e4m3x2_to_f16x2(r3), c3 = e4m3x2_to_f16x2(r3 >> 16);
+#pragma unroll
+            for (int nh = 0; nh < NH; ++nh) {
+              mma16816<MT>(acc[d][nh], a0, a1, a2, a3, pb[tt][nh][0], pb[tt][nh][1]);
+              mma16816<MT>(acc[d + 1][nh], c0, c1, c2, c3, pb[tt][nh][0], pb[tt][nh][1]);
+            }
           }
         }
-      }
-    }
-    if constexpr (FP8) {
-      // One k32 MMA covers the stage's 32 tokens.  Cache bytes past the context may hold anything (NaN
-      // codes included): clear them.  mk[h] masks this lane's four tokens of half h.
-      uint32_t mk[2] = {0xffffffffu, 0xffffffffu};
-      if (stage_tok0 + 32 > t_end) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int vt = stage_tok0 + h * 16 + 4 * qi;
-          mk[h] = (vt < t_end ? 0x000000ffu : 0u) | (vt + 1 < t_end ? 0x0000ff00u : 0u) |
-                  (vt + 2 < t_end ? 0x00ff0000u : 0u) | (vt + 3 < t_end ? 0xff000000u : 0u);
-        }
-      }
-#pragma unroll
-      for (int n = 0; n < NT; n += 2) {
-        uint32_t r0, r1, r2, r3;
-        ldmatrix_x4(stage + voff8 + (n / 2) * (16 * BS), r0, r1, r2, r3);
-        r0 &= mk[0]; r1 &= mk[1]; r2 &= mk[0]; r3 &= mk[1];
-        mma16832_e4m3(acc[n], pa_lo[0][0], pa_hi[0][0], pa_lo[1][0], pa_hi[1][0], r0, r1);
-        mma16832_e4m3(acc[n + 1], pa_lo[0][0], pa_hi[0][0], pa_lo[1][0], pa_hi[1][0], r2, r3);
-        mma16832_e4m3(acc[n], pa_lo[0][1], pa_hi[0][1], pa_lo[1][1], pa_hi[1][1], r0, r1);
-        mma16832_e4m3(acc[n + 1], pa_lo[0][1], pa_hi[0][1], pa_lo[1][1], pa_hi[1][1], r2, r3);
       }
     }
 
@@ -581,26 +526,33 @@ paged_decode_mma_kernel(const DecodeParams p) {
   }
 
   // ---- merge the warps' states
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+#pragma unroll
+  for (int nh = 0; nh < NH; ++nh) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+#pragma unroll
+      for (int o = 4; o <= 16; o <<= 1) l_run[nh][e] += __shfl_xor_sync(0xffffffffu, l_run[nh][e], o);
+    }
+  }
 
   __syncthreads();  // every warp is done with its ring: the merge buffer may alias it
-  float* macc = reinterpret_cast<float*>(smem);                    // [NW][16][ROW_F]
-  float* mml = macc + NW * 16 * C::ROW_F;                          // [NW][16][2] = (m, l)
-  {
-    float* a = macc + (warp * 16 + gi) * C::ROW_F + 2 * qi;
+  float* macc = reinterpret_cast<float*>(smem);                    // [NW][16 heads][ROW_F]
+  float* mml = macc + NW * 16 * C::ROW_F;                          // [NW][16 heads][2] = (m, l)
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      *reinterpret_cast<float2*>(a + n * 8) = make_float2(acc[n][0], acc[n][1]);
-      if (rows16) *reinterpret_cast<float2*>(a + 8 * C::ROW_F + n * 8) = make_float2(acc[n][2], acc[n][3]);
-    }
-    if (qi == 0) {
-      mml[(warp * 16 + gi) * 2 + 0] = m_lo;
-      mml[(warp * 16 + gi) * 2 + 1] = l_lo;
-      mml[(warp * 16 + gi + 8) * 2 + 0] = m_hi;
-      mml[(warp * 16 + gi + 8) * 2 + 1] = l_hi;
+  for (int nh = 0; nh < NH; ++nh) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = nh * 8 + 2 * qi + e;
+      float* a = macc + (warp * 16 + h) * C::ROW_F + gi;
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        a[d * 16] = acc[d][nh][e];
+        a[d * 16 + 8] = acc[d][nh][2 + e];
+      }
+      if (gi == 0) {
+        mml[(warp * 16 + h) * 2 + 0] = m_run[nh][e];
+        mml[(warp * 16 + h) * 2 + 1] = l_run[nh][e];
+      }
     }
   }
   __syncthreads();
@@ -634,12 +586,16 @@ paged_decode_mma_kernel(const DecodeParams p) {
         T* o = reinterpret_cast<T*>(p.out) + (static_cast<int64_t>(seq) * p.num_heads + head) * HEAD + d;
         *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
       } else {
-        const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.max_parts + part;
+        const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.max_parts + first;
         T* o = reinterpret_cast<T*>(p.tmp_out) + slot * HEAD + d;
         *reinterpret_cast<uint32_t*>(o) = pack2<T>(n0 * inv, n1 * inv);
         if (d == 0) {
           p.max_logits[slot] = M;   // log2 domain
           p.exp_sums[slot] = den;
+          for (int k = 1; k < my_chunks; ++k) {   // the partitions folded into this one carry no weight
+            p.max_logits[slot + k] = -INFINITY;
+            p.exp_sums[slot + k] = 0.f;
+          }
         }
       }
     }
@@ -723,7 +679,8 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
   mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
   float sum = 0.f;
   for (int j = threadIdx.x; j < nparts; j += 128) {
-    const float w = exp_sums[slot0 + j] * exp2_approx(max_logits[slot0 + j] - mx);
+    const float e = exp_sums[slot0 + j];
+    const float w = e != 0.f ? e * exp2_approx(max_logits[slot0 + j] - mx) : 0.f;   // slots folded into a neighbour
     wgt[j] = w;
     sum += w;
   }
@@ -743,7 +700,7 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
 #pragma unroll
     for (int k = 0; k < PER_LANE; ++k) {
       const int d = lane + k * 32;
-      if (d < HEAD) a[k] += w * to_f32<T>(tp[static_cast<int64_t>(j) * HEAD + d]);
+      if (d < HEAD && w != 0.f) a[k] += w * to_f32<T>(tp[static_cast<int64_t>(j) * HEAD + d]);
     }
   }
 #pragma unroll

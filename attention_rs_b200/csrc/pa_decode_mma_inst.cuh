@@ -8,10 +8,10 @@
 
 namespace pa {
 
-template <typename T, bool FP8, int HEAD, int BS>
-int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
-  using C = DecodeCfg<T, FP8, HEAD, BS>;
-  auto kernel = paged_decode_mma_kernel<T, FP8, HEAD, BS>;
+template <typename T, bool FP8, int HEAD, int BS, int NH>
+int launch_decode_mma_nh(const DecodeParams& p, cudaStream_t stream) {
+  using C = DecodeCfg<T, FP8, HEAD, BS, NH>;
+  auto kernel = paged_decode_mma_kernel<T, FP8, HEAD, BS, NH>;
   // Opt in to the large dynamic shared-memory carve-out once per device instead
   // of on every call (the reference sets it per call, src/kernels/src/pagedattention.cu:570-573).
   static bool configured[64] = {};
@@ -22,10 +22,11 @@ int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
       return PA_ERR_CUDA;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int gsplit = (p.group + 15) / 16;
+  const int gsplit = (p.group + 8 * NH - 1) / (8 * NH);
   const bool partitioned = p.partition_size > 0;
   const int csize = partitioned ? 1 : (p.cluster < 1 ? 1 : p.cluster);
-  dim3 grid(p.num_kv_heads * gsplit, p.num_seqs, partitioned ? p.max_parts : csize);
+  const int ppc = p.parts_per_cta < 1 ? 1 : p.parts_per_cta;
+  dim3 grid(p.num_kv_heads * gsplit, p.num_seqs, partitioned ? (p.max_parts + ppc - 1) / ppc : csize);
   if (csize > 1) {
     // Single pass over a long context: a thread-block cluster splits it and merges through distributed
     // shared memory, so no scratch buffer and no second launch are needed.
@@ -65,6 +66,13 @@ int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
       return PA_ERR_CUDA;
   }
   return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+// Groups of up to 8 query heads per kv head take one n-tile of heads per CTA, larger groups two.
+template <typename T, bool FP8, int HEAD, int BS>
+int launch_decode_mma_one(const DecodeParams& p, cudaStream_t stream) {
+  return p.group <= 8 ? launch_decode_mma_nh<T, FP8, HEAD, BS, 1>(p, stream)
+                      : launch_decode_mma_nh<T, FP8, HEAD, BS, 2>(p, stream);
 }
 
 template <typename T, bool FP8, int HEAD>

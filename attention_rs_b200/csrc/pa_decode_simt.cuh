@@ -143,7 +143,7 @@ paged_decode_merge_generic_kernel(T* __restrict__ out, const float* __restrict__
   float mx = -INFINITY;
   for (int j = 0; j < nparts; ++j) mx = fmaxf(mx, max_logits[slot0 + j]);
   float sum = 0.f;
-  for (int j = 0; j < nparts; ++j) sum += exp_sums[slot0 + j] * exp2f(max_logits[slot0 + j] - mx);
+  for (int j = 0; j < nparts; ++j) sum += exp_sums[slot0 + j] * exp2f(max_logits[slot0 + j] - mx);   // this path fills every slot
   for (int d = threadIdx.x; d < head_size; d += blockDim.x) {
     float a = 0.f;
     for (int j = 0; j < nparts; ++j)

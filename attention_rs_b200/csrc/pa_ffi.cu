@@ -106,11 +106,26 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
   p.cluster = 1;
   if (!a.partitioned) {
     const int chunks = (a.max_context_len + PA_PARTITION_SIZE - 1) / PA_PARTITION_SIZE;
-    const long pairs = static_cast<long>(a.num_seqs) * a.num_kv_heads * ((p.group + 15) / 16);
+    const long pairs = static_cast<long>(a.num_seqs) * a.num_kv_heads * ((p.group + 15) / 16);  // CTAs at cluster size 1
     while (p.cluster < 8 && p.cluster * 2 <= chunks && pairs * p.cluster < 592) p.cluster *= 2;
     if (const char* e = getenv("PA_V1_CLUSTER")) {   // tuning override
       const int v = atoi(e);
       if (v == 1 || v == 2 || v == 4 || v == 8) p.cluster = v;
+    }
+  }
+  // Partitioned: a CTA streams best when it moves about half a megabyte, so consecutive partitions are
+  // folded into one CTA (two for 16-bit caches at d128, four for FP8) as long as the grid stays large
+  // enough to balance: measured at the benchmark shapes.
+  p.parts_per_cta = 1;
+  if (a.partitioned) {
+    const long part_bytes = 2L * PA_PARTITION_SIZE * a.head_size * kvsize;
+    const long ctas = static_cast<long>(a.num_seqs) * a.num_kv_heads * ((p.group + 15) / 16) * p.max_parts;
+    while (p.parts_per_cta < 4 && part_bytes * p.parts_per_cta < 512 * 1024 && p.parts_per_cta * 2 <= p.max_parts &&
+           ctas / (p.parts_per_cta * 2) >= 6000)
+      p.parts_per_cta *= 2;
+    if (const char* e = getenv("PA_V2_PARTS_PER_CTA")) {   // tuning override
+      const int v = atoi(e);
+      if (v == 1 || v == 2 || v == 4 || v == 8) p.parts_per_cta = v;
     }
   }
   p.scale = a.scale;
