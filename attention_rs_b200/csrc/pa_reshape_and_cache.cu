@@ -103,42 +103,48 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
   }
   __syncthreads();
 
-  // ---- keys: one 16-byte chunk of the cache per thread-iteration
+  // ---- keys: one 16-byte chunk of the cache per thread-iteration, flat over (token, chunk) so that
+  // every thread has work and several independent loads are in flight
   const int cph = head_size / X;  // chunks per head
-  const int chunk_lo = row_lo / X, chunk_hi = row_hi / X;
-  for (int c = chunk_lo + tid; c < chunk_hi; c += RC_THREADS) {
-    const int h = c / cph, ci = c % cph;
+  const int chunk_lo = row_lo / X, nchunk = row_hi / X - chunk_lo;
+  const int kwork = ntok * nchunk;
 #pragma unroll 4
-    for (int j = 0; j < ntok; ++j) {
-      const int64_t blk = s_blk[j];
-      if (blk < 0) continue;
-      const S* src = key + (tok0 + j) * key_stride + c * X;
-      Pack<D, X> outv;
-      if constexpr (!QUANT) {
-        outv = *reinterpret_cast<const Pack<D, X>*>(src);
-      } else {
-        const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src);
+  for (int idx = tid; idx < kwork; idx += RC_THREADS) {
+    const int j = idx / nchunk, c = chunk_lo + idx % nchunk;
+    const int64_t blk = s_blk[j];
+    if (blk < 0) continue;
+    const int h = c / cph, ci = c % cph;
+    const S* src = key + (tok0 + j) * key_stride + c * X;
+    Pack<D, X> outv;
+    if constexpr (!QUANT) {
+      outv = *reinterpret_cast<const Pack<D, X>*>(src);
+    } else {
+      const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src);
 #pragma unroll
-        for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
-      }
-      D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
-      *reinterpret_cast<Pack<D, X>*>(dst) = outv;
+      for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
     }
+    D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
+    *reinterpret_cast<Pack<D, X>*>(dst) = outv;
   }
 
-  // ---- values: rows of the cache
+  // ---- values: a thread owns two adjacent rows of the cache (two adjacent source elements: one load)
   const int ngroups = s_ngroups;
   const unsigned single = s_single;
-  for (int row = row_lo + tid; row < row_hi; row += RC_THREADS) {
+  const unsigned all_tokens = ntok >= 32 ? 0xffffffffu : ((1u << ntok) - 1u);
+  for (int row = row_lo + 2 * tid; row < row_hi; row += 2 * RC_THREADS) {
     const S* src = value + tok0 * value_stride + row;
-    // tokens alone in their block: one element each, loads independent of one another
+    // tokens alone in their block: one element per row, loads independent of one another
 #pragma unroll 8
     for (int j = 0; j < ntok; ++j) {
-      if (single & (1u << j))
-        value_cache[(s_blk[j] * n + row) * BS + s_off[j]] = convert_elem<S, D, QUANT>(src[j * value_stride], v_scale);
+      if (single & (1u << j)) {
+        const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + j * value_stride);
+        D* dst = value_cache + (s_blk[j] * n + row) * BS + s_off[j];
+        dst[0] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+        dst[BS] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+      }
     }
-    if (single == (ntok >= 32 ? 0xffffffffu : ((1u << ntok) - 1u))) continue;
-    // blocks that receive several tokens: aligned pieces of the row go out as one wide store
+    if (single == all_tokens) continue;
+    // blocks that receive several tokens: aligned pieces of the two rows go out as wide stores
     for (int g = 0; g < ngroups; ++g) {
       const unsigned mask = g_mask[g];
       if ((mask & (mask - 1u)) == 0u) continue;
@@ -149,16 +155,23 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
         const unsigned sub = (mask >> (pc * PIECE)) & FULL;
         if (sub == 0u) continue;
         if (sub == FULL) {
-          Pack<D, PIECE> outv;
+          Pack<D, PIECE> out0, out1;
 #pragma unroll
-          for (int e = 0; e < PIECE; ++e)
-            outv.v[e] = convert_elem<S, D, QUANT>(src[g_map[g][pc * PIECE + e] * value_stride], v_scale);
-          *reinterpret_cast<Pack<D, PIECE>*>(dst + pc * PIECE) = outv;
+          for (int e = 0; e < PIECE; ++e) {
+            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
+            out0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+            out1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+          }
+          *reinterpret_cast<Pack<D, PIECE>*>(dst + pc * PIECE) = out0;
+          *reinterpret_cast<Pack<D, PIECE>*>(dst + BS + pc * PIECE) = out1;
         } else {
 #pragma unroll
           for (int e = 0; e < PIECE; ++e)
-            if (sub & (1u << e))
-              dst[pc * PIECE + e] = convert_elem<S, D, QUANT>(src[g_map[g][pc * PIECE + e] * value_stride], v_scale);
+            if (sub & (1u << e)) {
+              const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
+              dst[pc * PIECE + e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+              dst[BS + pc * PIECE + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+            }
         }
       }
     }
@@ -197,7 +210,8 @@ int launch_typed(const ReshapeArgs& a, cudaStream_t stream) {
                        ((a.key_stride * sizeof(S)) % (X * sizeof(S)) == 0) &&
                        (reinterpret_cast<uintptr_t>(a.key_cache) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(a.value_cache) % 16 == 0);
-  const bool fast = aligned && a.x == X && a.head_size % X == 0 &&
+  const bool vpair = reinterpret_cast<uintptr_t>(a.value) % (2 * sizeof(S)) == 0 && a.value_stride % 2 == 0;
+  const bool fast = aligned && vpair && a.x == X && a.head_size % X == 0 &&
                     (a.block_size == 8 || a.block_size == 16 || a.block_size == 32);
   if (a.num_tokens <= 0) return PA_OK;
   if (fast) {

@@ -1,6 +1,6 @@
 """Benchmark of the paged decode-attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 2|4|5] [--gather]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 1|2|3|4|5] [--gather]
 
 One step = one decode-attention pass (the partitioned entry point of the C ABI: main kernel plus
 partition merge) over one batch of the workload.  Metric: effective KV-cache read bandwidth in GB/s
@@ -38,9 +38,9 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic KV bytes of the decode kernel, from the ncu
 # capture summarised in profiles/paged_decode_mma_bf16_d128_bs16_ncu_full_16seq.md (a 16-sequence slice of
-# the headline workload: 357.17 MB read + 4.33 MB written for 356.53 MB of KV).  Traffic grows in
+# the headline workload: 357.22 MB read + 3.96 MB written for 356.53 MB of KV).  Traffic grows in
 # proportion to the KV bytes processed, so a launch's traffic is this ratio times its algorithmic bytes.
-NCU_TRAFFIC_RATIO = {2: 1.0139}
+NCU_TRAFFIC_RATIO = {2: 1.0130}
 
 
 def measured_peak():
@@ -231,13 +231,46 @@ def run_ours(args):
     e2e_ms = e0.elapsed_time(e1)
     h2d = h_in.numel()
     d2h = h_out.numel() * h_out.element_size()
+
+    # The same step captured once in a CUDA graph and replayed: one launch per step instead of five.
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                d_in = h_in.to(dev, non_blocking=True)
+                pa.reshape_and_cache(view(d_in, "k"), view(d_in, "v"), kc, vc, view(d_in, "slots"),
+                                     k_scale if fp8 else 1.0, v_scale if fp8 else 1.0)
+                o = pa.paged_attention(view(d_in, "q"), kc, vc, view(d_in, "bt"), view(d_in, "cl"), slopes, mcl,
+                                       w.scale, w.softcapping, k_scale, v_scale)
+                h_out.copy_(o, non_blocking=True)
+            for _ in range(3):
+                g.replay()
+                side.synchronize()
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(side)
+            for _ in range(e2e_steps):
+                g.replay()
+                side.synchronize()
+            g1.record(side)
+            side.synchronize()
+            graph_ms = g0.elapsed_time(g1)
+        torch.cuda.current_stream().wait_stream(side)
+    except Exception as exc:  # the plain end-to-end figure above stands on its own
+        graph_ms = None
+        sys.stderr.write(f"[bench] CUDA-graph replay of the step not measured: {exc!r}\n")
+    barrier()
     clocks = sampler.stop() if sampler is not None else None
 
     # ---- max over ranks
     if dist is not None:
-        tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms, e2e_ms, graph_ms if graph_ms is not None else -1.0], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(tt[0]), float(tt[1])
+        graph_ms = float(tt[2]) if graph_ms is not None else None
         kvb = torch.tensor([w.kv_bytes()], device=dev, dtype=torch.float64)
         dist.all_reduce(kvb, op=dist.ReduceOp.SUM)
         total_kv = float(kvb[0])
@@ -259,8 +292,12 @@ def run_ours(args):
             "pct_of_8TBps_nominal_per_gpu": round(100.0 * per_gpu / NOMINAL_HBM_GBS, 2),
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 5),
-                    "path": "pinned host -> device copies, reshape_and_cache of the step's tokens, paged_attention, "
-                            "output copied back to pinned host memory"},
+                    "path": "pinned host -> device copy of the step's inputs, reshape_and_cache of the step's tokens, "
+                            "paged_attention, output copied back to pinned host memory, stream synchronised",
+                    "cuda_graph_replay": (None if graph_ms is None else
+                                          {"value": round(total_kv / (graph_ms / e2e_steps * 1e-3) / 1e9, 1), "unit": UNIT,
+                                           "ms_per_step": round(graph_ms / e2e_steps, 5),
+                                           "note": "the same step captured once and replayed"})},
             "gpu_launches": args.steps * 2,
             "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(per_gpu / peak, 4), "peak_kind": f"of {peak_kind}",
@@ -411,13 +448,67 @@ def time_reference_kernels(w, t, ref_gpu, reps: int = 20):
     return res
 
 
+def run_scatter(args):
+    """Configuration 3: reshape_and_cache of 32768 tokens into random free slots (and, for context, the
+    consecutive-slot pattern of a real prefill).  Metric: algorithmic bytes (key / value rows read + cache
+    bytes written + slot mapping) / time."""
+    import torch
+    import attention_rs_b200 as pa
+    from attention_rs_b200 import workloads
+    rank, world, local = dist_env()
+    if world > 1:
+        raise SystemExit("--config 3 is a single-GPU measurement")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    out = {}
+    sampler = ClockSampler(local).start()
+    for label, contiguous in (("random_slots", False), ("consecutive_slots", True)):
+        w = workloads.scatter_workload(contiguous=contiguous)
+        g = torch.Generator(device=dev)
+        g.manual_seed(w.seed)
+        key = torch.randn((w.num_tokens, w.num_heads, w.head_size), generator=g, device=dev).to(torch.bfloat16)
+        value = torch.randn((w.num_tokens, w.num_heads, w.head_size), generator=g, device=dev).to(torch.bfloat16)
+        slots = torch.from_numpy(w.slot_mapping).to(dev)
+        kshape, vshape = workloads.cache_shapes(w.num_blocks, w.num_heads, w.head_size, w.block_size, "bf16")
+        kc = torch.zeros(kshape, dtype=torch.bfloat16, device=dev)
+        vc = torch.zeros(vshape, dtype=torch.bfloat16, device=dev)
+        for _ in range(max(args.warmup, 3)):
+            pa.reshape_and_cache(key, value, kc, vc, slots)
+        torch.cuda.synchronize()
+        steps = min(args.steps, 500)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            pa.reshape_and_cache(key, value, kc, vc, slots)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        out[label] = {"ms_per_step": round(ms, 5), "GBps": round(w.algorithmic_bytes() / ms / 1e6, 1),
+                      "algorithmic_bytes": w.algorithmic_bytes(), "steps": steps}
+    clocks = sampler.stop()
+    peak, kind = measured_peak()
+    main_ = out["random_slots"]
+    line = {"metric": "reshape_and_cache_effective_bandwidth", "value": main_["GBps"], "unit": UNIT, "n_gpus": 1,
+            "steps": main_["steps"], "warmup": max(args.warmup, 3), "ms_per_step": main_["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "cfg3: reshape_and_cache, 16 x 2048 tokens, 8 kv heads, head_dim 128, block_size 16, "
+                                   "65536-slot pool, ~2% padding, seeded random free slots",
+                       "l2": "sources (128 MiB) + caches (256 MiB) exceed the 126 MB L2"},
+            "roofline": {"bound": "hbm", "achieved": main_["GBps"], "peak": peak, "unit": "GB/s",
+                         "frac": round(main_["GBps"] / peak, 4), "peak_kind": f"of {kind}", "traffic": None,
+                         "algorithmic_bytes_per_launch": main_["algorithmic_bytes"]},
+            "variants": out, "gpu_launches": main_["steps"], "clocks": clocks,
+            "e2e": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 4, 5])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="shrink the batch (same shapes and length distribution); for profiler captures only")
     ap.add_argument("--gather", action="store_true", help="all-gather the outputs inside the timed step (N > 1)")
@@ -425,7 +516,9 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline leg")
     ap.add_argument("--ref-budget", type=float, default=90.0, help="seconds for all steps of --impl reference")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.config == 3:
+        run_scatter(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
