@@ -19,6 +19,8 @@
 //    one 16-byte store; isolated tokens fall back to single-element stores.
 // A scalar kernel covers shapes the fast path does not take (block sizes other
 // than 8 / 16 / 32, x * sizeof(element) != 16, misaligned views).
+#include <stdlib.h>
+
 #include "pa_common.cuh"
 #include "pa_launch.h"
 
@@ -50,6 +52,10 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
                          D* __restrict__ value_cache, const int64_t* __restrict__ slot_mapping, int num_tokens,
                          int num_heads, int head_size, int64_t key_stride, int64_t value_stride, float k_scale,
                          float v_scale, int tokens_per_cta) {
+  // gridDim.z = number of passes: pass z handles the tokens whose destination block is congruent to z.  CTAs
+  // are dispatched pass by pass, so at any time only 1/passes of the cache is being written and partially
+  // written 32-byte sectors stay in L2 until the other tokens of their block arrive, instead of being
+  // evicted and read back (what a scatter of tokens to random slots otherwise costs).
   constexpr int X = 16 / sizeof(D);                 // cache elements per 16-byte key chunk
   constexpr int PIECE = X < BS ? X : BS;            // elements of a value row written by one wide store
   constexpr int NPIECE = BS / PIECE;
@@ -76,7 +82,7 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
     int off = 0;
     if (lane < ntok) {
       const int64_t slot = slot_mapping[tok0 + lane];
-      if (slot >= 0) { blk = slot / BS; off = static_cast<int>(slot % BS); }
+      if (slot >= 0 && (slot / BS) % gridDim.z == blockIdx.z) { blk = slot / BS; off = static_cast<int>(slot % BS); }
     }
     s_blk[lane] = blk;
     s_off[lane] = off;
@@ -103,6 +109,8 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
   }
   __syncthreads();
 
+  if (s_ngroups == 0) return;  // no token of this CTA falls in this pass
+
   // ---- keys: one 16-byte chunk of the cache per thread-iteration, flat over (token, chunk) so that
   // every thread has work and several independent loads are in flight
   const int cph = head_size / X;  // chunks per head
@@ -127,52 +135,56 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
     *reinterpret_cast<Pack<D, X>*>(dst) = outv;
   }
 
-  // ---- values: a thread owns two adjacent rows of the cache (two adjacent source elements: one load)
+  // ---- values.  A thread owns two adjacent rows of the cache (two adjacent source elements: one load).
   const int ngroups = s_ngroups;
   const unsigned single = s_single;
-  const unsigned all_tokens = ntok >= 32 ? 0xffffffffu : ((1u << ntok) - 1u);
-  for (int row = row_lo + 2 * tid; row < row_hi; row += 2 * RC_THREADS) {
-    const S* src = value + tok0 * value_stride + row;
-    // tokens alone in their block: one element per row, loads independent of one another
+  // tokens alone in their block: one element per row, loads independent of one another
+  if (single != 0u) {
+    for (int row = row_lo + 2 * tid; row < row_hi; row += 2 * RC_THREADS) {
+      const S* src = value + tok0 * value_stride + row;
 #pragma unroll 8
-    for (int j = 0; j < ntok; ++j) {
-      if (single & (1u << j)) {
-        const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + j * value_stride);
-        D* dst = value_cache + (s_blk[j] * n + row) * BS + s_off[j];
-        dst[0] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-        dst[BS] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+      for (int j = 0; j < ntok; ++j) {
+        if (single & (1u << j)) {
+          const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + j * value_stride);
+          D* dst = value_cache + (s_blk[j] * n + row) * BS + s_off[j];
+          dst[0] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+          dst[BS] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+        }
       }
     }
-    if (single == all_tokens) continue;
-    // blocks that receive several tokens: aligned pieces of the two rows go out as wide stores
-    for (int g = 0; g < ngroups; ++g) {
-      const unsigned mask = g_mask[g];
-      if ((mask & (mask - 1u)) == 0u) continue;
-      D* dst = value_cache + (g_blk[g] * n + row) * BS;
+  }
+  // blocks that receive several tokens: aligned pieces of a row go out as one wide store each.  Work items
+  // are (row pair, piece) with the piece index fastest, so neighbouring lanes complete each other's sectors.
+  const int npair = (row_hi - row_lo) / 2;
+  for (int g = 0; g < ngroups; ++g) {
+    const unsigned mask = g_mask[g];
+    if ((mask & (mask - 1u)) == 0u) continue;
+    D* base = value_cache + g_blk[g] * n * BS;
+    for (int item = tid; item < npair * NPIECE; item += RC_THREADS) {
+      const int row = row_lo + 2 * (item / NPIECE), pc = item % NPIECE;
+      constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
+      const unsigned sub = (mask >> (pc * PIECE)) & FULL;
+      if (sub == 0u) continue;
+      const S* src = value + tok0 * value_stride + row;
+      D* dst = base + static_cast<int64_t>(row) * BS + pc * PIECE;
+      if (sub == FULL) {
+        Pack<D, PIECE> out0, out1;
 #pragma unroll
-      for (int pc = 0; pc < NPIECE; ++pc) {
-        constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
-        const unsigned sub = (mask >> (pc * PIECE)) & FULL;
-        if (sub == 0u) continue;
-        if (sub == FULL) {
-          Pack<D, PIECE> out0, out1;
-#pragma unroll
-          for (int e = 0; e < PIECE; ++e) {
-            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
-            out0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-            out1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
-          }
-          *reinterpret_cast<Pack<D, PIECE>*>(dst + pc * PIECE) = out0;
-          *reinterpret_cast<Pack<D, PIECE>*>(dst + BS + pc * PIECE) = out1;
-        } else {
-#pragma unroll
-          for (int e = 0; e < PIECE; ++e)
-            if (sub & (1u << e)) {
-              const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
-              dst[pc * PIECE + e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-              dst[BS + pc * PIECE + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
-            }
+        for (int e = 0; e < PIECE; ++e) {
+          const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
+          out0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+          out1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
         }
+        *reinterpret_cast<Pack<D, PIECE>*>(dst) = out0;
+        *reinterpret_cast<Pack<D, PIECE>*>(dst + BS) = out1;
+      } else {
+#pragma unroll
+        for (int e = 0; e < PIECE; ++e)
+          if (sub & (1u << e)) {
+            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
+            dst[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+            dst[BS + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+          }
       }
     }
   }
@@ -224,7 +236,16 @@ int launch_typed(const ReshapeArgs& a, cudaStream_t stream) {
     const int max_split = (n / X + RC_THREADS - 1) / RC_THREADS;          // at least one chunk per thread
     int gy = (592 + gx - 1) / gx;
     gy = gy < 1 ? 1 : (gy > max_split ? max_split : gy);
-    const dim3 grid(gx, gy);
+    // Passes over the destination blocks (see the kernel): enough that the part of the cache one pass can
+    // touch, at worst one sector per element, stays well inside the L2.
+    const double worst_bytes = static_cast<double>(a.num_tokens) * n * 36.0;
+    int passes = static_cast<int>(worst_bytes / (96.0 * 1024 * 1024)) + 1;
+    passes = passes > 8 ? 8 : passes;
+    if (const char* e = getenv("PA_RESHAPE_PASSES")) {   // tuning override
+      const int v = atoi(e);
+      if (v >= 1 && v <= 64) passes = v;
+    }
+    const dim3 grid(gx, gy, passes);
 #define PA_RC_GO(BS)                                                                                               \
   reshape_and_cache_kernel<S, D, QUANT, BS><<<grid, RC_THREADS, 0, stream>>>(                                      \
       key, value, kc, vc, a.slot_mapping, a.num_tokens, a.num_heads, a.head_size, a.key_stride, a.value_stride,   \

@@ -485,6 +485,24 @@ def run_scatter(args):
         ms = a.elapsed_time(b) / steps
         out[label] = {"ms_per_step": round(ms, 5), "GBps": round(w.algorithmic_bytes() / ms / 1e6, 1),
                       "algorithmic_bytes": w.algorithmic_bytes(), "steps": steps}
+        if args.impl == "reference":
+            # Extra context for this configuration: the reference's own kernel, compiled unchanged, same inputs.
+            try:
+                from oracle import ref_gpu
+                if ref_gpu.available():
+                    for _ in range(3):
+                        ref_gpu.reshape_and_cache(key, value, kc, vc, slots)
+                    torch.cuda.synchronize()
+                    a.record()
+                    for _ in range(50):
+                        ref_gpu.reshape_and_cache(key, value, kc, vc, slots)
+                    b.record()
+                    torch.cuda.synchronize()
+                    rms = a.elapsed_time(b) / 50
+                    out[label]["reference_cuda_kernel"] = {"ms_per_step": round(rms, 5),
+                                                           "GBps": round(w.algorithmic_bytes() / rms / 1e6, 1)}
+            except Exception as exc:
+                out[label]["reference_cuda_kernel"] = {"unavailable": repr(exc)}
     clocks = sampler.stop()
     peak, kind = measured_peak()
     main_ = out["random_slots"]
