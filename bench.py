@@ -309,7 +309,7 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(w, t, budget_s=args.cpu_budget)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -413,7 +413,7 @@ def run_reference(args):
             line["reference_cuda_kernels"] = time_reference_kernels(w, t, ref_gpu)
     except Exception as exc:  # the CPU number above stands on its own
         line["reference_cuda_kernels"] = {"unavailable": repr(exc)}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def time_reference_kernels(w, t, ref_gpu, reps: int = 20):
@@ -517,10 +517,33 @@ def run_scatter(args):
                          "algorithmic_bytes_per_launch": main_["algorithmic_bytes"]},
             "variants": out, "gpu_launches": main_["steps"], "clocks": clocks,
             "e2e": None}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = None
+
+
+def _claim_stdout():
+    """Keeps stdout for the one JSON line: everything else that writes to file descriptor 1 (NCCL's version
+    banner, library chatter) is sent to stderr instead."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
 
 
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
