@@ -12,7 +12,8 @@
 // tokens per CTA when the call is small, so that a decode step's handful of tokens
 // still spreads over the SMs):
 //  * keys move as whole 16-byte chunks (x elements), one load and one store each;
-//  * for values the CTA first groups its tokens by destination block.  Along a
+//  * value rows are staged in shared memory with 16-byte loads, then the CTA groups
+//    its tokens by destination block.  Along a
 //    value-cache row the tokens of one block are adjacent, so wherever a group
 //    fills an aligned 16-byte piece of a row (the normal case for a prefill whose
 //    slots run consecutively) the piece is gathered in registers and written with
@@ -111,82 +112,97 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
 
   if (s_ngroups == 0) return;  // no token of this CTA falls in this pass
 
-  // ---- keys: one 16-byte chunk of the cache per thread-iteration, flat over (token, chunk) so that
-  // every thread has work and several independent loads are in flight
-  const int cph = head_size / X;  // chunks per head
-  const int chunk_lo = row_lo / X, nchunk = row_hi / X - chunk_lo;
-  const int kwork = ntok * nchunk;
-#pragma unroll 4
-  for (int idx = tid; idx < kwork; idx += RC_THREADS) {
-    const int j = idx / nchunk, c = chunk_lo + idx % nchunk;
-    const int64_t blk = s_blk[j];
-    if (blk < 0) continue;
-    const int h = c / cph, ci = c % cph;
-    const S* src = key + (tok0 + j) * key_stride + c * X;
-    Pack<D, X> outv;
-    if constexpr (!QUANT) {
-      outv = *reinterpret_cast<const Pack<D, X>*>(src);
-    } else {
-      const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src);
-#pragma unroll
-      for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
-    }
-    D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
-    *reinterpret_cast<Pack<D, X>*>(dst) = outv;
-  }
-
-  // ---- values.  A thread owns two adjacent rows of the cache (two adjacent source elements: one load).
+  // The CTA walks its columns in slices of 512 bytes per token: the value rows of a slice are staged in
+  // shared memory with 16-byte loads (every thread has several independent loads in flight), then written
+  // to the cache from there; keys go straight from global to global, 16 bytes at a time.
+  constexpr int SLICE = 512 / sizeof(S);              // source elements per token and slice
+  constexpr int VEC = 16 / sizeof(S);                 // source elements per 16-byte load
+  __shared__ __align__(16) S s_val[RC_TOKENS][SLICE];
+  const int cph = head_size / X;                      // key chunks per head
   const int ngroups = s_ngroups;
   const unsigned single = s_single;
-  // tokens alone in their block: one element per row, loads independent of one another
-  if (single != 0u) {
-    for (int row = row_lo + 2 * tid; row < row_hi; row += 2 * RC_THREADS) {
-      const S* src = value + tok0 * value_stride + row;
-#pragma unroll 8
-      for (int j = 0; j < ntok; ++j) {
-        if (single & (1u << j)) {
-          const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + j * value_stride);
-          D* dst = value_cache + (s_blk[j] * n + row) * BS + s_off[j];
-          dst[0] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-          dst[BS] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
-        }
-      }
+
+  for (int cs = row_lo; cs < row_hi; cs += SLICE) {
+    const int cols = min(SLICE, row_hi - cs);         // a multiple of X, hence of VEC
+    // ---- stage the value rows of this pass's tokens
+    const int vec_per_tok = cols / VEC;
+    for (int idx = tid; idx < ntok * vec_per_tok; idx += RC_THREADS) {
+      const int j = idx / vec_per_tok, v = idx % vec_per_tok;
+      if (s_blk[j] < 0) continue;
+      *reinterpret_cast<uint4*>(&s_val[j][v * VEC]) =
+          *reinterpret_cast<const uint4*>(value + (tok0 + j) * value_stride + cs + v * VEC);
     }
-  }
-  // blocks that receive several tokens: aligned pieces of a row go out as one wide store each.  Work items
-  // are (row pair, piece) with the piece index fastest, so neighbouring lanes complete each other's sectors.
-  const int npair = (row_hi - row_lo) / 2;
-  for (int g = 0; g < ngroups; ++g) {
-    const unsigned mask = g_mask[g];
-    if ((mask & (mask - 1u)) == 0u) continue;
-    D* base = value_cache + g_blk[g] * n * BS;
-    for (int item = tid; item < npair * NPIECE; item += RC_THREADS) {
-      const int row = row_lo + 2 * (item / NPIECE), pc = item % NPIECE;
-      constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
-      const unsigned sub = (mask >> (pc * PIECE)) & FULL;
-      if (sub == 0u) continue;
-      const S* src = value + tok0 * value_stride + row;
-      D* dst = base + static_cast<int64_t>(row) * BS + pc * PIECE;
-      if (sub == FULL) {
-        Pack<D, PIECE> out0, out1;
-#pragma unroll
-        for (int e = 0; e < PIECE; ++e) {
-          const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
-          out0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-          out1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
-        }
-        *reinterpret_cast<Pack<D, PIECE>*>(dst) = out0;
-        *reinterpret_cast<Pack<D, PIECE>*>(dst + BS) = out1;
+    // ---- keys: one 16-byte chunk of the cache per thread-iteration, flat over (token, chunk)
+    const int chunk_lo = cs / X, nchunk = cols / X;
+#pragma unroll 4
+    for (int idx = tid; idx < ntok * nchunk; idx += RC_THREADS) {
+      const int j = idx / nchunk, c = chunk_lo + idx % nchunk;
+      const int64_t blk = s_blk[j];
+      if (blk < 0) continue;
+      const int h = c / cph, ci = c % cph;
+      const S* src = key + (tok0 + j) * key_stride + c * X;
+      Pack<D, X> outv;
+      if constexpr (!QUANT) {
+        outv = *reinterpret_cast<const Pack<D, X>*>(src);
       } else {
+        const Pack<S, X> in = *reinterpret_cast<const Pack<S, X>*>(src);
 #pragma unroll
-        for (int e = 0; e < PIECE; ++e)
-          if (sub & (1u << e)) {
-            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(src + g_map[g][pc * PIECE + e] * value_stride);
-            dst[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-            dst[BS + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+        for (int e = 0; e < X; ++e) outv.v[e] = convert_elem<S, D, true>(in.v[e], k_scale);
+      }
+      D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
+      *reinterpret_cast<Pack<D, X>*>(dst) = outv;
+    }
+    __syncthreads();
+
+    // ---- values out of shared memory.  A thread owns two adjacent rows of the cache.
+    // tokens alone in their block: one element per row
+    if (single != 0u) {
+      for (int r = 2 * tid; r < cols; r += 2 * RC_THREADS) {
+#pragma unroll 8
+        for (int j = 0; j < ntok; ++j) {
+          if (single & (1u << j)) {
+            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(&s_val[j][r]);
+            D* dst = value_cache + (s_blk[j] * n + cs + r) * BS + s_off[j];
+            dst[0] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+            dst[BS] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
           }
+        }
       }
     }
+    // blocks that receive several tokens: aligned pieces of a row go out as one wide store each.  Work items
+    // are (row pair, piece) with the piece index fastest, so neighbouring lanes complete each other's sectors.
+    for (int g = 0; g < ngroups; ++g) {
+      const unsigned mask = g_mask[g];
+      if ((mask & (mask - 1u)) == 0u) continue;
+      D* base = value_cache + (g_blk[g] * n + cs) * BS;
+      for (int item = tid; item < (cols / 2) * NPIECE; item += RC_THREADS) {
+        const int r = 2 * (item / NPIECE), pc = item % NPIECE;
+        constexpr unsigned FULL = PIECE >= 32 ? 0xffffffffu : ((1u << PIECE) - 1u);
+        const unsigned sub = (mask >> (pc * PIECE)) & FULL;
+        if (sub == 0u) continue;
+        D* dst = base + static_cast<int64_t>(r) * BS + pc * PIECE;
+        if (sub == FULL) {
+          Pack<D, PIECE> out0, out1;
+#pragma unroll
+          for (int e = 0; e < PIECE; ++e) {
+            const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(&s_val[g_map[g][pc * PIECE + e]][r]);
+            out0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+            out1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+          }
+          *reinterpret_cast<Pack<D, PIECE>*>(dst) = out0;
+          *reinterpret_cast<Pack<D, PIECE>*>(dst + BS) = out1;
+        } else {
+#pragma unroll
+          for (int e = 0; e < PIECE; ++e)
+            if (sub & (1u << e)) {
+              const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(&s_val[g_map[g][pc * PIECE + e]][r]);
+              dst[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+              dst[BS + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+            }
+        }
+      }
+    }
+    __syncthreads();  // the next slice reuses the staging buffer
   }
 }
 
@@ -222,7 +238,7 @@ int launch_typed(const ReshapeArgs& a, cudaStream_t stream) {
                        ((a.key_stride * sizeof(S)) % (X * sizeof(S)) == 0) &&
                        (reinterpret_cast<uintptr_t>(a.key_cache) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(a.value_cache) % 16 == 0);
-  const bool vpair = reinterpret_cast<uintptr_t>(a.value) % (2 * sizeof(S)) == 0 && a.value_stride % 2 == 0;
+  const bool vpair = reinterpret_cast<uintptr_t>(a.value) % 16 == 0 && (a.value_stride * sizeof(S)) % 16 == 0;  // 16-byte loads
   const bool fast = aligned && vpair && a.x == X && a.head_size % X == 0 &&
                     (a.block_size == 8 || a.block_size == 16 || a.block_size == 32);
   if (a.num_tokens <= 0) return PA_OK;
