@@ -52,6 +52,12 @@ struct DecodeParams {
   const uint32_t* block_tables;
   const uint32_t* context_lens;
   const float* alibi_slopes;  // may be null
+  // Fused append (may be null): the key / value rows of the token at position context_len - 1 of every
+  // sequence, [num_seqs, num_kv_heads, HEAD] in the query dtype, row strides in elements.  The CTA that
+  // reaches that token writes the rows into the caches (quantising for an FP8 cache) and uses them.
+  const void* new_key;
+  const void* new_value;
+  int64_t new_key_stride, new_value_stride;
   unsigned* status;
   int64_t kv_block_stride;    // elements
   int64_t kv_head_stride;     // elements
@@ -154,6 +160,7 @@ paged_decode_mma_kernel(const DecodeParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const uint32_t ring = smem_addr(smem) + warp * (STAGES * STAGE_BYTES);
+  unsigned char* ring_ptr = smem + warp * (STAGES * STAGE_BYTES);
   const uint32_t bars = smem_addr(smem) + C::DATA_BYTES + warp * (STAGES * 16);  // [stage]{K,V}
 
   if (ctx == 0 && csize == 1) {
@@ -344,6 +351,32 @@ paged_decode_mma_kernel(const DecodeParams p) {
     healthy = __all_sync(0xffffffffu, mbar_wait(bk, par, p.status));
     if (!healthy) break;
 
+    // Fused append: the stage that holds the sequence's newest token takes its key / value rows from the
+    // step's inputs (the copy just loaded from the cache is stale there) and stores them to the cache.
+    const int tn = ctx - 1;
+    const bool patch = p.new_key != nullptr && tn >= stage_tok0 && tn < stage_tok0 + STOK;
+    if (patch) {
+      constexpr int XK = 16 / C::ES;  // cache elements per 16-byte key chunk
+      const int bi = (tn - stage_tok0) / BS, off = tn % BS;
+      const int64_t phys = static_cast<int64_t>(table[tn / BS]);
+      const T* nk = reinterpret_cast<const T*>(p.new_key) + static_cast<int64_t>(seq) * p.new_key_stride + kvh * HEAD;
+      unsigned char* gk = const_cast<unsigned char*>(kc) + (phys * p.kv_block_stride + head_off) * C::ES;
+      unsigned char* sk = ring_ptr + s * STAGE_BYTES + bi * TILE_BYTES;
+      for (int c = lane; c < HEAD / XK; c += 32) {
+        uint4 chunk;
+        if constexpr (!FP8) {
+          chunk = *reinterpret_cast<const uint4*>(nk + c * XK);
+        } else {
+          unsigned char* b = reinterpret_cast<unsigned char*>(&chunk);
+#pragma unroll
+          for (int e = 0; e < XK; ++e) b[e] = f32_to_e4m3(__fdiv_rn(to_f32<T>(nk[c * XK + e]), p.k_scale));
+        }
+        *reinterpret_cast<uint4*>(sk + (c * BS + off) * 16) = chunk;
+        if (blockIdx.x % gsplit == 0) *reinterpret_cast<uint4*>(gk + (c * BS + off) * 16) = chunk;
+      }
+      __syncwarp();
+    }
+
 #ifdef PA_DEBUG_SKIP_COMPUTE
     // Measurement aid (never defined in a product build): stream the tiles and do no arithmetic, which
     // gives the bandwidth ceiling of this access pattern.
@@ -473,6 +506,22 @@ paged_decode_mma_kernel(const DecodeParams p) {
     // ---------------- O^T += V^T P^T
     healthy = __all_sync(0xffffffffu, mbar_wait(bv, par, p.status));
     if (!healthy) break;
+    if (patch) {
+      using CE = std::conditional_t<FP8, unsigned char, T>;  // cache element
+      const int bi = (tn - stage_tok0) / BS, off = tn % BS;
+      const int64_t phys = static_cast<int64_t>(table[tn / BS]);
+      const T* nv = reinterpret_cast<const T*>(p.new_value) + static_cast<int64_t>(seq) * p.new_value_stride + kvh * HEAD;
+      CE* gv = reinterpret_cast<CE*>(const_cast<unsigned char*>(vc) + (phys * p.kv_block_stride + head_off) * C::ES);
+      CE* sv = reinterpret_cast<CE*>(ring_ptr + s * STAGE_BYTES + (SB + bi) * TILE_BYTES);
+      for (int d = lane; d < HEAD; d += 32) {
+        CE v;
+        if constexpr (!FP8) v = nv[d];
+        else v = f32_to_e4m3(__fdiv_rn(to_f32<T>(nv[d]), p.v_scale));
+        sv[d * BS + off] = v;
+        if (blockIdx.x % gsplit == 0) gv[d * BS + off] = v;
+      }
+      __syncwarp();
+    }
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
       const int tile_tok0 = stage_tok0 + tt * 16;

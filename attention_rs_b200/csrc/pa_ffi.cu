@@ -53,6 +53,57 @@ int launch_simt(const DecodeParams& p, const AttnArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
 }
 
+// Scatter of each sequence's newest token (position context_len - 1) into the caches, for the paths that
+// cannot fold it into the attention kernel.  One CTA per sequence, one element per thread-iteration;
+// same layouts and FP8 rule as reshape_and_cache.
+template <typename T, typename CE>
+__global__ void append_rows_kernel(const T* __restrict__ key, const T* __restrict__ value, CE* __restrict__ key_cache,
+                                   CE* __restrict__ value_cache, const uint32_t* __restrict__ block_tables,
+                                   const uint32_t* __restrict__ context_lens, int max_num_blocks_per_seq, int num_kv_heads,
+                                   int head_size, int block_size, int64_t key_stride, int64_t value_stride,
+                                   int64_t kv_block_stride, int64_t kv_head_stride, float k_scale, float v_scale) {
+  const int seq = blockIdx.x;
+  const int ctx = static_cast<int>(context_lens[seq]);
+  if (ctx == 0) return;
+  const int tn = ctx - 1, off = tn % block_size;
+  const int64_t blk = block_tables[static_cast<int64_t>(seq) * max_num_blocks_per_seq + tn / block_size];
+  constexpr int x = 16 / static_cast<int>(sizeof(CE));
+  for (int i = threadIdx.x; i < num_kv_heads * head_size; i += blockDim.x) {
+    const int h = i / head_size, d = i % head_size;
+    const int64_t base = blk * kv_block_stride + static_cast<int64_t>(h) * kv_head_stride;
+    const T kv = key[seq * key_stride + i], vv = value[seq * value_stride + i];
+    CE ke, ve;
+    if constexpr (sizeof(CE) == sizeof(T)) {
+      ke = kv;
+      ve = vv;
+    } else {
+      ke = f32_to_e4m3(__fdiv_rn(to_f32<T>(kv), k_scale));
+      ve = f32_to_e4m3(__fdiv_rn(to_f32<T>(vv), v_scale));
+    }
+    key_cache[base + (static_cast<int64_t>(d / x) * block_size + off) * x + d % x] = ke;
+    value_cache[base + static_cast<int64_t>(d) * block_size + off] = ve;
+  }
+}
+
+template <typename T, typename CE>
+int launch_append(const AttnArgs& a, cudaStream_t stream) {
+  append_rows_kernel<T, CE><<<a.num_seqs, 256, 0, stream>>>(
+      reinterpret_cast<const T*>(a.new_key), reinterpret_cast<const T*>(a.new_value),
+      reinterpret_cast<CE*>(const_cast<void*>(a.key_cache)), reinterpret_cast<CE*>(const_cast<void*>(a.value_cache)),
+      a.block_tables, a.context_lens, a.max_num_blocks_per_seq, a.num_kv_heads, a.head_size, a.block_size,
+      a.new_key_stride, a.new_value_stride, a.kv_block_stride, a.kv_head_stride, a.k_scale, a.v_scale);
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+int launch_append_any(const AttnArgs& a, cudaStream_t stream) {
+  const bool fp8 = a.kv_dtype == DT_FP8;
+  if (a.dtype == DT_F16) return fp8 ? launch_append<__half, uint8_t>(a, stream) : launch_append<__half, __half>(a, stream);
+  if (a.dtype == DT_BF16)
+    return fp8 ? launch_append<__nv_bfloat16, uint8_t>(a, stream) : launch_append<__nv_bfloat16, __nv_bfloat16>(a, stream);
+  if (a.dtype == DT_F32) return fp8 ? launch_append<float, uint8_t>(a, stream) : launch_append<float, float>(a, stream);
+  return PA_ERR_UNSUPPORTED;
+}
+
 bool force_simt() {
   static const int v = [] {
     const char* e = getenv("PA_FORCE_SIMT");
@@ -87,6 +138,10 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
   p.block_tables = a.block_tables;
   p.context_lens = a.context_lens;
   p.alibi_slopes = a.alibi_slopes;
+  p.new_key = a.new_key;
+  p.new_value = a.new_value;
+  p.new_key_stride = a.new_key_stride;
+  p.new_value_stride = a.new_value_stride;
   p.status = device_status_word();
   if (p.status == nullptr) return fail(PA_ERR_CUDA, "cannot resolve the device status word");
   p.kv_block_stride = a.kv_block_stride;
@@ -139,13 +194,31 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
                        (a.kv_block_stride * kvsize) % 16 == 0 && (a.kv_head_stride * kvsize) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(a.query) % 4 == 0 && reinterpret_cast<uintptr_t>(a.out) % 4 == 0 &&
                        a.q_stride % 2 == 0 && (!a.partitioned || reinterpret_cast<uintptr_t>(a.tmp_out) % 4 == 0);
-  if (qsize == 2 && aligned && !force_simt()) {
+  // The tensor-core kernel folds the append of the step's token in when its rows can be read 16 bytes at a time.
+  const bool append = a.new_key != nullptr;
+  const bool append_aligned = !append || (reinterpret_cast<uintptr_t>(a.new_key) % 16 == 0 &&
+                                          reinterpret_cast<uintptr_t>(a.new_value) % 16 == 0 &&
+                                          (a.new_key_stride * qsize) % 16 == 0 && (a.new_value_stride * qsize) % 16 == 0);
+  if (qsize == 2 && aligned && append_aligned && !force_simt()) {
     int rc = PA_ERR_UNSUPPORTED;
     if (a.dtype == DT_BF16 && a.kv_dtype == DT_BF16) rc = launch_decode_mma_bf16(p, a.head_size, a.block_size, stream);
     else if (a.dtype == DT_F16 && a.kv_dtype == DT_F16) rc = launch_decode_mma_f16(p, a.head_size, a.block_size, stream);
     else if (a.dtype == DT_BF16 && a.kv_dtype == DT_FP8) rc = launch_decode_mma_bf16_fp8(p, a.head_size, a.block_size, stream);
     else if (a.dtype == DT_F16 && a.kv_dtype == DT_FP8) rc = launch_decode_mma_f16_fp8(p, a.head_size, a.block_size, stream);
     if (rc != PA_ERR_UNSUPPORTED) return rc == PA_OK ? rc : fail(rc, "kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  if (append) {   // generic route: scatter the token first, then attend over the updated cache
+    const int arc = launch_append_any(a, stream);
+    if (arc != PA_OK) return fail(arc, "append launch failed (%d)", arc);
+    p.new_key = p.new_value = nullptr;
+    if (qsize == 2 && aligned && !force_simt()) {
+      int rc2 = PA_ERR_UNSUPPORTED;
+      if (a.dtype == DT_BF16 && a.kv_dtype == DT_BF16) rc2 = launch_decode_mma_bf16(p, a.head_size, a.block_size, stream);
+      else if (a.dtype == DT_F16 && a.kv_dtype == DT_F16) rc2 = launch_decode_mma_f16(p, a.head_size, a.block_size, stream);
+      else if (a.dtype == DT_BF16 && a.kv_dtype == DT_FP8) rc2 = launch_decode_mma_bf16_fp8(p, a.head_size, a.block_size, stream);
+      else if (a.dtype == DT_F16 && a.kv_dtype == DT_FP8) rc2 = launch_decode_mma_f16_fp8(p, a.head_size, a.block_size, stream);
+      if (rc2 != PA_ERR_UNSUPPORTED) return rc2 == PA_OK ? rc2 : fail(rc2, "kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
   }
   int rc = PA_ERR_UNSUPPORTED;
   if (a.dtype == DT_F32 && a.kv_dtype == DT_F32) rc = launch_simt<float, float>(p, a, stream);
@@ -195,7 +268,8 @@ void call_reshape_and_cache(void* key, void* value, void* key_cache, void* value
 }
 
 static int attention_entry(bool partitioned, void* out, float* exp_sums, float* max_logits, void* tmp_out,
-                           const void* query, const void* key_cache, const void* value_cache, int32_t num_kv_heads,
+                           const void* query, const void* new_key, const void* new_value, int32_t new_key_stride,
+                           int32_t new_value_stride, const void* key_cache, const void* value_cache, int32_t num_kv_heads,
                            float scale, const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
                            int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
                            int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
@@ -219,6 +293,12 @@ static int attention_entry(bool partitioned, void* out, float* exp_sums, float* 
   a.block_tables = block_tables;
   a.context_lens = context_lens;
   a.alibi_slopes = alibi_slopes;
+  a.new_key = new_key;
+  a.new_value = new_value;
+  a.new_key_stride = new_key_stride;
+  a.new_value_stride = new_value_stride;
+  if ((new_key == nullptr) != (new_value == nullptr))
+    return fail(PA_ERR_INVALID_ARGUMENT, "key and value rows must be given together");
   a.num_kv_heads = num_kv_heads;
   a.num_seqs = num_seqs;
   a.num_heads = num_heads;
@@ -246,7 +326,7 @@ int paged_attention_v1_ex(void* out, const void* query, const void* key_cache, c
                           int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
                           const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
                           int64_t stream) {
-  return attention_entry(false, out, nullptr, nullptr, nullptr, query, key_cache, value_cache, num_kv_heads, scale,
+  return attention_entry(false, out, nullptr, nullptr, nullptr, query, nullptr, nullptr, 0, 0, key_cache, value_cache, num_kv_heads, scale,
                          block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
                          max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
                          alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
@@ -259,7 +339,7 @@ int paged_attention_v2_ex(void* out, float* exp_sums, float* max_logits, void* t
                           int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
                           int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
                           uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream) {
-  return attention_entry(true, out, exp_sums, max_logits, tmp_out, query, key_cache, value_cache, num_kv_heads, scale,
+  return attention_entry(true, out, exp_sums, max_logits, tmp_out, query, nullptr, nullptr, 0, 0, key_cache, value_cache, num_kv_heads, scale,
                          block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
                          max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
                          alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
@@ -286,6 +366,35 @@ void paged_attention_v2(void* out, float* exp_sums, float* max_logits, void* tmp
                               block_tables, context_lens, block_size, max_context_len, num_seqs, num_heads, head_size,
                               max_num_blocks_per_seq, q_stride, kv_block_stride, kv_head_stride, dtype, softscapping,
                               nullptr, dtype, 1.f, 1.f, stream);
+}
+
+int paged_decode_step_v1(void* out, const void* query, const void* key, const void* value, int32_t key_stride,
+                         int32_t value_stride, void* key_cache, void* value_cache, int32_t num_kv_heads, float scale,
+                         const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
+                         int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                         int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
+                         int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
+                         uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream) {
+  if (num_seqs > 0 && (!key || !value)) return fail(PA_ERR_INVALID_ARGUMENT, "null key / value rows passed to paged_decode_step");
+  return attention_entry(false, out, nullptr, nullptr, nullptr, query, key, value, key_stride, value_stride, key_cache,
+                         value_cache, num_kv_heads, scale, block_tables, context_lens, block_size, max_context_len,
+                         num_seqs, num_heads, head_size, max_num_blocks_per_seq, q_stride, kv_block_stride,
+                         kv_head_stride, dtype, softscapping, alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
+}
+
+int paged_decode_step_v2(void* out, float* exp_sums, float* max_logits, void* tmp_out, const void* query,
+                         const void* key, const void* value, int32_t key_stride, int32_t value_stride, void* key_cache,
+                         void* value_cache, int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                         const uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                         int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                         int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                         const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
+                         int64_t stream) {
+  if (num_seqs > 0 && (!key || !value)) return fail(PA_ERR_INVALID_ARGUMENT, "null key / value rows passed to paged_decode_step");
+  return attention_entry(true, out, exp_sums, max_logits, tmp_out, query, key, value, key_stride, value_stride, key_cache,
+                         value_cache, num_kv_heads, scale, block_tables, context_lens, block_size, max_context_len,
+                         num_seqs, num_heads, head_size, max_num_blocks_per_seq, q_stride, kv_block_stride,
+                         kv_head_stride, dtype, softscapping, alibi_slopes, kv_cache_dtype, k_scale, v_scale, stream);
 }
 
 const char* pa_last_error(void) { return t_error; }

@@ -63,10 +63,11 @@ int pa_paged_attention_uses_partitions(int64_t num_seqs, int64_t num_heads, int6
   return parts > 1 ? 1 : 0;
 }
 
-int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_tensor* value_cache,
-                       const pa_tensor* block_tables, const pa_tensor* context_lens, const pa_tensor* alibi_slopes,
-                       int64_t max_context_len, float softmax_scale, float softcapping, float k_scale, float v_scale,
-                       const pa_tensor* out, void* workspace, size_t workspace_bytes, int64_t stream) {
+static int paged_attention_impl(const pa_tensor* q, const pa_tensor* new_key, const pa_tensor* new_value,
+                                const pa_tensor* key_cache, const pa_tensor* value_cache, const pa_tensor* block_tables,
+                                const pa_tensor* context_lens, const pa_tensor* alibi_slopes, int64_t max_context_len,
+                                float softmax_scale, float softcapping, float k_scale, float v_scale,
+                                const pa_tensor* out, void* workspace, size_t workspace_bytes, int64_t stream) {
   if (!q || !key_cache || !value_cache || !block_tables || !context_lens || !out)
     return fail(PA_ERR_INVALID_ARGUMENT, "null tensor descriptor");
   if (!float_dtype(q->dtype)) return fail(PA_ERR_INVALID_ARGUMENT, "dtype code %u is not supported", q->dtype);
@@ -137,6 +138,18 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
   if (!fits_i32(q->stride[0]) || !fits_i32(key_cache->stride[0]) || !fits_i32(key_cache->stride[1]) ||
       !fits_i32(max_context_len) || !fits_i32(max_blocks))
     return fail(PA_ERR_INVALID_ARGUMENT, "a stride or size does not fit the 32-bit fields of the kernel interface");
+  // Fused decode step: the rows of each sequence's newest token.
+  const bool step = new_key != nullptr || new_value != nullptr;
+  if (step) {
+    if (!new_key || !new_value) return fail(PA_ERR_INVALID_ARGUMENT, "key and value rows must be given together");
+    for (const pa_tensor* t : {new_key, new_value}) {
+      if (t->dtype != q->dtype || t->rank != 3 || t->shape[0] != num_seqs || t->shape[1] != num_kv_heads ||
+          t->shape[2] != head_size || t->stride[2] != 1 || t->stride[1] != head_size || !fits_i32(t->stride[0]))
+        return fail(PA_ERR_INVALID_ARGUMENT,
+                    "decode-step key / value must be [num_seqs, num_kv_heads, head_size] tensors of q's dtype, "
+                    "contiguous in their last two dimensions");
+    }
+  }
 
   const bool want_parts = pa_paged_attention_uses_partitions(num_seqs, num_heads, num_kv_heads, max_context_len) != 0;
   const size_t need = pa_paged_attention_workspace_bytes(num_seqs, num_heads, head_size, max_context_len, q->dtype);
@@ -151,6 +164,16 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
     void* tmp_out = w;
     float* exp_sums = reinterpret_cast<float*>(w + up(num_seqs * num_heads * nparts * head_size * pa::dtype_size(q->dtype)));
     float* max_logits = reinterpret_cast<float*>(reinterpret_cast<char*>(exp_sums) + up(num_seqs * num_heads * nparts * 4));
+    if (step)
+      return paged_decode_step_v2(out->data, exp_sums, max_logits, tmp_out, q->data, new_key->data, new_value->data,
+                                  (int32_t)new_key->stride[0], (int32_t)new_value->stride[0], key_cache->data,
+                                  value_cache->data, (int32_t)num_kv_heads, softmax_scale,
+                                  static_cast<const uint32_t*>(block_tables->data),
+                                  static_cast<const uint32_t*>(context_lens->data), (int32_t)block_size,
+                                  (int32_t)max_context_len, (int32_t)num_seqs, (int32_t)num_heads, (int32_t)head_size,
+                                  (int32_t)max_blocks, (int32_t)q->stride[0], (int32_t)key_cache->stride[0],
+                                  (int32_t)key_cache->stride[1], q->dtype, softcapping, slopes, kv_dtype, k_scale,
+                                  v_scale, stream);
     return paged_attention_v2_ex(out->data, exp_sums, max_logits, tmp_out, q->data, key_cache->data, value_cache->data,
                                  (int32_t)num_kv_heads, softmax_scale, static_cast<const uint32_t*>(block_tables->data),
                                  static_cast<const uint32_t*>(context_lens->data), (int32_t)block_size,
@@ -159,6 +182,15 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
                                  (int32_t)key_cache->stride[1], q->dtype, softcapping, slopes, kv_dtype, k_scale, v_scale,
                                  stream);
   }
+  if (step)
+    return paged_decode_step_v1(out->data, q->data, new_key->data, new_value->data, (int32_t)new_key->stride[0],
+                                (int32_t)new_value->stride[0], key_cache->data, value_cache->data, (int32_t)num_kv_heads,
+                                softmax_scale, static_cast<const uint32_t*>(block_tables->data),
+                                static_cast<const uint32_t*>(context_lens->data), (int32_t)block_size,
+                                (int32_t)max_context_len, (int32_t)num_seqs, (int32_t)num_heads, (int32_t)head_size,
+                                (int32_t)max_blocks, (int32_t)q->stride[0], (int32_t)key_cache->stride[0],
+                                (int32_t)key_cache->stride[1], q->dtype, softcapping, slopes, kv_dtype, k_scale, v_scale,
+                                stream);
   return paged_attention_v1_ex(out->data, q->data, key_cache->data, value_cache->data, (int32_t)num_kv_heads, softmax_scale,
                                static_cast<const uint32_t*>(block_tables->data),
                                static_cast<const uint32_t*>(context_lens->data), (int32_t)block_size,
@@ -166,6 +198,26 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
                                (int32_t)max_blocks, (int32_t)q->stride[0], (int32_t)key_cache->stride[0],
                                (int32_t)key_cache->stride[1], q->dtype, softcapping, slopes, kv_dtype, k_scale, v_scale,
                                stream);
+}
+
+int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_tensor* value_cache,
+                       const pa_tensor* block_tables, const pa_tensor* context_lens, const pa_tensor* alibi_slopes,
+                       int64_t max_context_len, float softmax_scale, float softcapping, float k_scale, float v_scale,
+                       const pa_tensor* out, void* workspace, size_t workspace_bytes, int64_t stream) {
+  return paged_attention_impl(q, nullptr, nullptr, key_cache, value_cache, block_tables, context_lens, alibi_slopes,
+                              max_context_len, softmax_scale, softcapping, k_scale, v_scale, out, workspace,
+                              workspace_bytes, stream);
+}
+
+int pa_decode_step(const pa_tensor* q, const pa_tensor* key, const pa_tensor* value, const pa_tensor* key_cache,
+                   const pa_tensor* value_cache, const pa_tensor* block_tables, const pa_tensor* context_lens,
+                   const pa_tensor* alibi_slopes, int64_t max_context_len, float softmax_scale, float softcapping,
+                   float k_scale, float v_scale, const pa_tensor* out, void* workspace, size_t workspace_bytes,
+                   int64_t stream) {
+  if (!key || !value) return fail(PA_ERR_INVALID_ARGUMENT, "null tensor descriptor");
+  return paged_attention_impl(q, key, value, key_cache, value_cache, block_tables, context_lens, alibi_slopes,
+                              max_context_len, softmax_scale, softcapping, k_scale, v_scale, out, workspace,
+                              workspace_bytes, stream);
 }
 
 int pa_reshape_and_cache(const pa_tensor* key, const pa_tensor* value, const pa_tensor* key_cache,

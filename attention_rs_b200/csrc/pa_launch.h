@@ -32,6 +32,9 @@ struct AttnArgs {
   const uint32_t* block_tables;
   const uint32_t* context_lens;
   const float* alibi_slopes;
+  const void* new_key;      // fused append: rows of each sequence's newest token (null: plain attention)
+  const void* new_value;
+  int64_t new_key_stride, new_value_stride;  // elements
   int num_kv_heads, num_seqs, num_heads, head_size, block_size;
   int max_context_len, max_num_blocks_per_seq, q_stride;
   int64_t kv_block_stride, kv_head_stride;  // elements

@@ -67,6 +67,12 @@ def load_library() -> ctypes.CDLL:
     L.pa_static_scratch_needed.argtypes = [i32, i32, i32, i32, u32]
     L.pa_paged_attention.restype = ctypes.c_int
     L.pa_paged_attention.argtypes = [tp, tp, tp, tp, tp, tp, i64, f32, f32, f32, f32, tp, vp, ctypes.c_size_t, i64]
+    L.pa_decode_step.restype = ctypes.c_int
+    L.pa_decode_step.argtypes = [tp, tp, tp, tp, tp, tp, tp, tp, i64, f32, f32, f32, f32, tp, vp, ctypes.c_size_t, i64]
+    L.paged_decode_step_v1.restype = ctypes.c_int
+    L.paged_decode_step_v1.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.paged_decode_step_v2.restype = ctypes.c_int
+    L.paged_decode_step_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
     L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t
     L.pa_paged_attention_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     L.pa_paged_attention_uses_partitions.restype = ctypes.c_int
@@ -179,6 +185,38 @@ def paged_attention(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch
                                   _ref(_desc(block_tables)), _ref(_desc(context_lens)), _ref(_desc(alibi_slopes)),
                                   int(max_context_len), float(softmax_scale), float(softcapping), float(k_scale),
                                   float(v_scale), _ref(_desc(out)), ws_ptr, ws_len, stream)
+    _check(rc)
+    return out
+
+
+def decode_step(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                value_cache: torch.Tensor, block_tables: torch.Tensor, context_lens: torch.Tensor,
+                alibi_slopes: Optional[torch.Tensor], max_context_len: int, softmax_scale: float,
+                softcapping: float = 1.0, k_scale: float = 1.0, v_scale: float = 1.0,
+                out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step in one call: writes each sequence's new key / value row into the caches and attends.
+
+    Equivalent to ``reshape_and_cache(key, value, ...)`` with the slot of position ``context_lens[i] - 1``
+    followed by ``paged_attention(...)`` (the order of the reference's layer, src/lib.rs:231-278), but the
+    scatter is folded into the attention kernel.  key, value: [num_seqs, num_kv_heads, head_size]."""
+    L = load_library()
+    dev = _require_cuda(q, key, value, key_cache, value_cache, block_tables, context_lens, alibi_slopes, out, workspace)
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        ws_ptr, ws_len = None, 0
+        if q.dim() == 3 and q.dtype in _FLOAT_CODES and key_cache.dim() == 5:
+            ns, nh, hs = q.shape
+            if uses_partitions(ns, nh, key_cache.shape[1], max_context_len):
+                need = workspace_bytes(ns, nh, hs, max_context_len, q.dtype)
+                if workspace is None or workspace.numel() * workspace.element_size() < need:
+                    workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+                ws_ptr, ws_len = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = L.pa_decode_step(_ref(_desc(q)), _ref(_desc(key)), _ref(_desc(value)), _ref(_desc(key_cache)),
+                              _ref(_desc(value_cache)), _ref(_desc(block_tables)), _ref(_desc(context_lens)),
+                              _ref(_desc(alibi_slopes)), int(max_context_len), float(softmax_scale), float(softcapping),
+                              float(k_scale), float(v_scale), _ref(_desc(out)), ws_ptr, ws_len, stream)
     _check(rc)
     return out
 

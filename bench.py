@@ -187,13 +187,11 @@ def run_ours(args):
         raise SystemExit("a kernel reported a timed-out wait; the measurement is void")
 
     # ---- end to end through the public operators: the step's inputs start in pinned host memory.
-    # A decode step's inputs (query, the new token's key / value rows, slot mapping, block tables, context
+    # A decode step's inputs (query, the new token's key / value rows, block tables, context
     # lengths) are staged in ONE pinned buffer and cross PCIe as one copy; the views below are what the
     # operators receive.  The KV cache itself is state that lives in HBM across steps, as in the reference.
     new_k = torch.randn((ns, w.num_kv_heads, hs), device=dev).to(q.dtype)
-    last = (cl.long() - 1).clamp_(min=0)
-    slots = (bt.long().gather(1, (last // w.block_size).unsqueeze(1)).squeeze(1) * w.block_size + last % w.block_size)
-    parts_in = [("q", q), ("k", new_k), ("v", new_k.flip(0).contiguous()), ("slots", slots), ("bt", bt), ("cl", cl)]
+    parts_in = [("q", q), ("k", new_k), ("v", new_k.flip(0).contiguous()), ("bt", bt), ("cl", cl)]
     offs, total = {}, 0
     for name, x in parts_in:
         offs[name] = (total, x.numel() * x.element_size(), x.dtype, tuple(x.shape))
@@ -211,10 +209,8 @@ def run_ours(args):
 
     def e2e_step():
         d_in = h_in.to(dev, non_blocking=True)
-        pa.reshape_and_cache(view(d_in, "k"), view(d_in, "v"), kc, vc, view(d_in, "slots"),
-                             k_scale if fp8 else 1.0, v_scale if fp8 else 1.0)
-        o = pa.paged_attention(view(d_in, "q"), kc, vc, view(d_in, "bt"), view(d_in, "cl"), slopes, mcl, w.scale,
-                               w.softcapping, k_scale, v_scale)
+        o = pa.decode_step(view(d_in, "q"), view(d_in, "k"), view(d_in, "v"), kc, vc, view(d_in, "bt"),
+                           view(d_in, "cl"), slopes, mcl, w.scale, w.softcapping, k_scale, v_scale)
         h_out.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()    # the caller consumes the result before the next step
 
@@ -241,10 +237,8 @@ def run_ours(args):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=side):
                 d_in = h_in.to(dev, non_blocking=True)
-                pa.reshape_and_cache(view(d_in, "k"), view(d_in, "v"), kc, vc, view(d_in, "slots"),
-                                     k_scale if fp8 else 1.0, v_scale if fp8 else 1.0)
-                o = pa.paged_attention(view(d_in, "q"), kc, vc, view(d_in, "bt"), view(d_in, "cl"), slopes, mcl,
-                                       w.scale, w.softcapping, k_scale, v_scale)
+                o = pa.decode_step(view(d_in, "q"), view(d_in, "k"), view(d_in, "v"), kc, vc, view(d_in, "bt"),
+                                   view(d_in, "cl"), slopes, mcl, w.scale, w.softcapping, k_scale, v_scale)
                 h_out.copy_(o, non_blocking=True)
             for _ in range(3):
                 g.replay()
@@ -292,8 +286,9 @@ def run_ours(args):
             "pct_of_8TBps_nominal_per_gpu": round(100.0 * per_gpu / NOMINAL_HBM_GBS, 2),
             "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": round(e2e_ms / e2e_steps, 5),
-                    "path": "pinned host -> device copy of the step's inputs, reshape_and_cache of the step's tokens, "
-                            "paged_attention, output copied back to pinned host memory, stream synchronised",
+                    "path": "pinned host -> device copy of the step's inputs (query, new key / value rows, block tables, "
+                            "context lengths), decode_step (append of the new token fused into the attention kernel), "
+                            "output copied back to pinned host memory, stream synchronised",
                     "cuda_graph_replay": (None if graph_ms is None else
                                           {"value": round(total_kv / (graph_ms / e2e_steps * 1e-3) / 1e9, 1), "unit": UNIT,
                                            "ms_per_step": round(graph_ms / e2e_steps, 5),

@@ -129,6 +129,33 @@ int paged_attention_v2_ex(void* out, float* exp_sums, float* max_logits, void* t
                           int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
                           uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream);
 
+/* One decode step in one call: scatter of the step's new token plus attention.
+ * Fuses what the reference's layer does as two launches, reshape_and_cache (src/lib.rs:231-239) then
+ * paged_attention (src/lib.rs:268-278), for the decode case of exactly one new token per sequence, that
+ * token being position context_lens[i] - 1 of sequence i (context_lens already counts it, as in the
+ * reference's call order).  key / value: [num_seqs, num_kv_heads, head_size] rows of the query dtype with
+ * row strides key_stride / value_stride; they are written to the slot the block table gives for that
+ * position (quantised for an FP8 cache, same rule as call_reshape_and_cache_ex) by the very CTA that
+ * attends over that position, so no separate scatter launch and no slot_mapping are needed.  Results
+ * (output and cache bytes) are identical to call_reshape_and_cache_ex followed by paged_attention_v1_ex /
+ * paged_attention_v2_ex.  Sequences with context_len == 0 append nothing. */
+int paged_decode_step_v1(void* out, const void* query, const void* key, const void* value, int32_t key_stride,
+                         int32_t value_stride, void* key_cache, void* value_cache, int32_t num_kv_heads, float scale,
+                         const uint32_t* block_tables, const uint32_t* context_lens, int32_t block_size,
+                         int32_t max_context_len, int32_t num_seqs, int32_t num_heads, int32_t head_size,
+                         int32_t max_num_blocks_per_seq, int32_t q_stride, int32_t kv_block_stride,
+                         int32_t kv_head_stride, uint32_t dtype, float softscapping, const float* alibi_slopes,
+                         uint32_t kv_cache_dtype, float k_scale, float v_scale, int64_t stream);
+
+int paged_decode_step_v2(void* out, float* exp_sums, float* max_logits, void* tmp_out, const void* query,
+                         const void* key, const void* value, int32_t key_stride, int32_t value_stride, void* key_cache,
+                         void* value_cache, int32_t num_kv_heads, float scale, const uint32_t* block_tables,
+                         const uint32_t* context_lens, int32_t block_size, int32_t max_context_len, int32_t num_seqs,
+                         int32_t num_heads, int32_t head_size, int32_t max_num_blocks_per_seq, int32_t q_stride,
+                         int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
+                         const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
+                         int64_t stream);
+
 /* Size of the scratch array built into the library for paged_attention_v2_static
  * (16 MiB; held on every GPU that loads the library, until the process exits). */
 #define PA_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
@@ -187,6 +214,16 @@ int pa_paged_attention(const pa_tensor* q, const pa_tensor* key_cache, const pa_
                        const pa_tensor* block_tables, const pa_tensor* context_lens, const pa_tensor* alibi_slopes,
                        int64_t max_context_len, float softmax_scale, float softcapping, float k_scale, float v_scale,
                        const pa_tensor* out, void* workspace, size_t workspace_bytes, int64_t stream);
+
+/* The decode step of the reference's attention layer in one call (src/lib.rs:231-278: reshape_and_cache of the
+ * step's token, then paged_attention): pa_paged_attention plus key / value, the [num_seqs, num_kv_heads,
+ * head_size] rows of each sequence's newest token (position context_lens[i] - 1).  Same checks, same result
+ * as pa_reshape_and_cache followed by pa_paged_attention; see paged_decode_step_v1. */
+int pa_decode_step(const pa_tensor* q, const pa_tensor* key, const pa_tensor* value, const pa_tensor* key_cache,
+                   const pa_tensor* value_cache, const pa_tensor* block_tables, const pa_tensor* context_lens,
+                   const pa_tensor* alibi_slopes, int64_t max_context_len, float softmax_scale, float softcapping,
+                   float k_scale, float v_scale, const pa_tensor* out, void* workspace, size_t workspace_bytes,
+                   int64_t stream);
 
 /* Bytes of scratch the partitioned path wants for these sizes: tmp_out + exp_sums +
  * max_logits as allocated at src/paged_attention.rs:199-203. */
