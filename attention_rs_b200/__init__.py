@@ -12,6 +12,7 @@ the shared library is present and the tensors live on a CUDA device.
 """
 from .ops import (  # noqa: F401
     PagedAttentionError,
+    copy_blocks,
     decode_step,
     library_path,
     load_library,

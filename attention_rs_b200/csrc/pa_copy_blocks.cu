@@ -1,0 +1,98 @@
+// copy_blocks for sm_100a: whole KV blocks copied src -> dst inside every layer's key and value cache
+// (copy-on-write / beam fork in the cache manager).
+//
+// Semantics of src/kernels/src/copy_blocks_kernel.cu:4-30 of the reference: grid (num_layers, num_pairs);
+// key_cache_ptrs / value_cache_ptrs are device arrays of per-layer cache base addresses; block_mapping is
+// [num_pairs][2] = (source block, destination block); numel_per_block elements per block and cache.
+// The reference exports one `extern "C" __global__` per element type and has no host launcher (its callers
+// load the kernels by name).  The same seven kernel names and signatures are defined here, so such callers
+// keep working, plus a host launcher for everyone else.  A block is one contiguous run, so the copy moves
+// 16 bytes per thread-iteration whenever the addresses allow (the reference moves one element), key and
+// value interleaved so that both streams are in flight, and a launch may split a pair over gridDim.z.
+#include "pa_common.cuh"
+#include "pa_launch.h"
+
+namespace {
+
+template <int ES>
+__device__ __forceinline__ void copy_blocks_body(const int64_t* key_cache_ptrs, const int64_t* value_cache_ptrs,
+                                                 const int64_t* __restrict__ block_mapping, int numel_per_block) {
+  const int layer = blockIdx.x, pair = blockIdx.y;
+  unsigned char* kc = reinterpret_cast<unsigned char*>(key_cache_ptrs[layer]);
+  unsigned char* vc = reinterpret_cast<unsigned char*>(value_cache_ptrs[layer]);
+  const int64_t src = block_mapping[2 * pair], dst = block_mapping[2 * pair + 1];
+  const int64_t bytes = static_cast<int64_t>(numel_per_block) * ES;
+  const unsigned char *ks = kc + src * bytes, *vs = vc + src * bytes;
+  unsigned char *kd = kc + dst * bytes, *vd = vc + dst * bytes;
+  // this CTA's share of the block when the launch splits pairs over gridDim.z (16-byte granular)
+  const int64_t per = ((bytes + gridDim.z - 1) / gridDim.z + 15) / 16 * 16;
+  const int64_t lo = min(bytes, per * blockIdx.z), hi = min(bytes, lo + per);
+  const bool vec = ((reinterpret_cast<uintptr_t>(ks) | reinterpret_cast<uintptr_t>(kd) | reinterpret_cast<uintptr_t>(vs) |
+                     reinterpret_cast<uintptr_t>(vd)) & 15) == 0;
+  if (vec) {
+    const int64_t nvec = (hi - lo) / 16;
+    const uint4* k4 = reinterpret_cast<const uint4*>(ks + lo);
+    const uint4* v4 = reinterpret_cast<const uint4*>(vs + lo);
+    uint4* kd4 = reinterpret_cast<uint4*>(kd + lo);
+    uint4* vd4 = reinterpret_cast<uint4*>(vd + lo);
+#pragma unroll 4
+    for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 a = k4[i], b = v4[i];
+      kd4[i] = a;
+      vd4[i] = b;
+    }
+    for (int64_t i = lo + nvec * 16 + threadIdx.x; i < hi; i += blockDim.x) {  // tail shorter than 16 bytes
+      kd[i] = ks[i];
+      vd[i] = vs[i];
+    }
+  } else {
+    for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      kd[i] = ks[i];
+      vd[i] = vs[i];
+    }
+  }
+}
+
+}  // namespace
+
+#define PA_COPY_BLOCKS_KERNEL(NAME, ES)                                                                         \
+  extern "C" __global__ void NAME(int64_t* key_cache_ptrs, int64_t* value_cache_ptrs,                         \
+                                  const int64_t* __restrict__ block_mapping, const int numel_per_block) {      \
+    copy_blocks_body<ES>(key_cache_ptrs, value_cache_ptrs, block_mapping, numel_per_block);                   \
+  }
+
+// Names and parameter lists of src/kernels/src/copy_blocks_kernel.cu:33-82.
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_u8, 1)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_u32, 4)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_i64, 8)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_f32, 4)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_f64, 8)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_f16, 2)
+PA_COPY_BLOCKS_KERNEL(copy_blocks_kernel_bf16, 2)
+
+extern "C" int pa_copy_blocks(const int64_t* key_cache_ptrs, const int64_t* value_cache_ptrs,
+                              const int64_t* block_mapping, int32_t num_layers, int32_t num_pairs,
+                              int32_t numel_per_block, int32_t elem_size, int64_t stream) {
+  if (num_layers == 0 || num_pairs == 0 || numel_per_block == 0) return PA_OK;
+  if (!key_cache_ptrs || !value_cache_ptrs || !block_mapping)
+    return pa::fail(PA_ERR_INVALID_ARGUMENT, "null pointer passed to pa_copy_blocks");
+  if (num_layers < 0 || num_pairs < 0 || numel_per_block < 0)
+    return pa::fail(PA_ERR_INVALID_ARGUMENT, "negative size passed to pa_copy_blocks");
+  if (num_pairs > 65535) return pa::fail(PA_ERR_UNSUPPORTED, "more than 65535 block pairs in one call");
+  // Enough CTAs to fill the GPU: split each pair's block over gridDim.z when there are few (layer, pair) items.
+  const int64_t bytes = static_cast<int64_t>(numel_per_block) * elem_size;
+  int split = 1;
+  while (static_cast<int64_t>(num_layers) * num_pairs * split < 592 && bytes / (split * 2) >= 8192 && split < 64) split *= 2;
+  const dim3 grid(num_layers, num_pairs, split);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int64_t* kp = const_cast<int64_t*>(key_cache_ptrs);
+  int64_t* vp = const_cast<int64_t*>(value_cache_ptrs);
+  switch (elem_size) {
+    case 1: copy_blocks_kernel_u8<<<grid, 256, 0, s>>>(kp, vp, block_mapping, numel_per_block); break;
+    case 2: copy_blocks_kernel_bf16<<<grid, 256, 0, s>>>(kp, vp, block_mapping, numel_per_block); break;
+    case 4: copy_blocks_kernel_f32<<<grid, 256, 0, s>>>(kp, vp, block_mapping, numel_per_block); break;
+    case 8: copy_blocks_kernel_f64<<<grid, 256, 0, s>>>(kp, vp, block_mapping, numel_per_block); break;
+    default: return pa::fail(PA_ERR_UNSUPPORTED, "element size %d not supported", elem_size);
+  }
+  return cudaGetLastError() == cudaSuccess ? PA_OK : pa::fail(PA_ERR_CUDA, "copy_blocks launch failed");
+}

@@ -73,6 +73,8 @@ def load_library() -> ctypes.CDLL:
     L.paged_decode_step_v1.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
     L.paged_decode_step_v2.restype = ctypes.c_int
     L.paged_decode_step_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.pa_copy_blocks.restype = ctypes.c_int
+    L.pa_copy_blocks.argtypes = [vp, vp, vp, i32, i32, i32, i32, i64]
     L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t
     L.pa_paged_attention_workspace_bytes.argtypes = [i64, i64, i64, i64, u32]
     L.pa_paged_attention_uses_partitions.restype = ctypes.c_int
@@ -236,6 +238,30 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = L.pa_reshape_and_cache(_ref(_desc(key)), _ref(_desc(value)), _ref(_desc(key_cache)), _ref(_desc(value_cache)),
                                     _ref(_desc(slot_mapping)), float(k_scale), float(v_scale), stream)
+    _check(rc)
+
+
+def copy_blocks(key_caches, value_caches, block_mapping: torch.Tensor) -> None:
+    """Copies whole KV blocks src -> dst in every layer's caches (mirror of the reference's copy_blocks kernels,
+    src/kernels/src/copy_blocks_kernel.cu).  key_caches / value_caches: lists of per-layer cache tensors of one
+    shape and dtype; block_mapping: int64 [num_pairs, 2] on the device."""
+    L = load_library()
+    dev = _require_cuda(block_mapping, *key_caches, *value_caches)
+    if len(key_caches) != len(value_caches) or not key_caches:
+        raise PagedAttentionError("key_caches and value_caches must be non-empty lists of equal length")
+    numel = key_caches[0][0].numel()
+    es = key_caches[0].element_size()
+    for t in list(key_caches) + list(value_caches):
+        if not t.is_contiguous() or t[0].numel() != numel or t.element_size() != es:
+            raise PagedAttentionError("every cache must be contiguous, with one block size and element size")
+    if block_mapping.dtype != torch.int64 or block_mapping.dim() != 2 or block_mapping.shape[1] != 2:
+        raise PagedAttentionError("block_mapping must be an int64 tensor of shape [num_pairs, 2]")
+    with torch.cuda.device(dev):
+        kp = torch.tensor([t.data_ptr() for t in key_caches], dtype=torch.int64, device=dev)
+        vp_ = torch.tensor([t.data_ptr() for t in value_caches], dtype=torch.int64, device=dev)
+        bm = block_mapping.contiguous()
+        rc = L.pa_copy_blocks(kp.data_ptr(), vp_.data_ptr(), bm.data_ptr(), len(key_caches), bm.shape[0], numel, es,
+                              torch.cuda.current_stream(dev).cuda_stream)
     _check(rc)
 
 

@@ -25,6 +25,7 @@
 #ifndef PAGEDATTENTION_B200_H_
 #define PAGEDATTENTION_B200_H_
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -155,6 +156,37 @@ int paged_decode_step_v2(void* out, float* exp_sums, float* max_logits, void* tm
                          int32_t kv_block_stride, int32_t kv_head_stride, uint32_t dtype, float softscapping,
                          const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
                          int64_t stream);
+
+/* copy_blocks: for every layer and every (source, destination) pair, copies one whole KV block inside the key
+ * cache and inside the value cache.  Host launcher for the reference's copy_blocks kernels
+ * (src/kernels/src/copy_blocks_kernel.cu:4-82), which the reference exports only as `extern "C" __global__`
+ * symbols copy_blocks_kernel_{u8,u32,i64,f32,f64,f16,bf16} with grid (num_layers, num_pairs); this library
+ * defines the same seven kernels (same names, same parameters) for callers that launch them by name.
+ * key_cache_ptrs / value_cache_ptrs: DEVICE arrays of num_layers cache base addresses; block_mapping: DEVICE
+ * int64 [num_pairs][2]; numel_per_block: elements per block and cache; elem_size: 1, 2, 4 or 8 bytes. */
+int pa_copy_blocks(const int64_t* key_cache_ptrs, const int64_t* value_cache_ptrs, const int64_t* block_mapping,
+                   int32_t num_layers, int32_t num_pairs, int32_t numel_per_block, int32_t elem_size, int64_t stream);
+
+/* Row-wise argsort: the fourteen asort_* symbols the reference's FFI declares (src/kernels/src/ffi.rs:75-186,
+ * defined in src/kernels/src/sort.cu:57-120).  x: [nrows, ncols] of the named type, dst: uint32 [nrows, ncols]
+ * receives, per row, the column indices in sorted order; if inplace, x's rows are sorted too.  Differences
+ * from the reference: all rows are sorted by the same launches, nothing synchronises the stream (the
+ * reference calls cudaStreamSynchronize), and equal keys keep their original order (the reference leaves
+ * ties unspecified).  Not part of the attention path: present for link compatibility. */
+void asort_asc_f32(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_f16(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_bf16(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_f64(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_u8(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_u32(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_asc_i64(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_f32(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_f16(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_bf16(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_f64(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_u8(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_u32(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
+void asort_desc_i64(void* x, void* dst, int nrows, int ncols, bool inplace, int64_t stream);
 
 /* Size of the scratch array built into the library for paged_attention_v2_static
  * (16 MiB; held on every GPU that loads the library, until the process exits). */

@@ -1,0 +1,56 @@
+"""copy_blocks on the GPU: bit-exact against a numpy restatement of the reference's kernel
+(src/kernels/src/copy_blocks_kernel.cu:4-30) and against the reference's own launch pattern."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_copy_blocks(key_caches, value_caches, mapping):
+    """For every layer and pair: key_cache[dst] = key_cache[src]; value_cache[dst] = value_cache[src]."""
+    for kc, vc in zip(key_caches, value_caches):
+        for src, dst in mapping:
+            kc[dst] = kc[src]
+            vc[dst] = vc[src]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32", "uint8", "int64"])
+@pytest.mark.parametrize("shape", [(12, 2, 64, 16), (9, 8, 128, 16), (7, 1, 80, 8), (6, 3, 5, 7)])
+def test_copy_blocks_bit_exact(dtype, shape):
+    import torch
+    import attention_rs_b200 as pa
+    dev = torch.device("cuda:0")
+    tdt = getattr(torch, dtype)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(hash(shape) % 1000 + len(dtype))
+    layers = 3
+    nb = shape[0]
+    nbytes = int(np.prod(shape)) * torch.empty((), dtype=tdt).element_size()
+    keys = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=g).view(tdt).reshape(shape).to(dev) for _ in range(layers)]
+    vals = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=g).view(tdt).reshape(shape).to(dev) for _ in range(layers)]
+    mapping = np.array([[0, 5], [1, 4], [2, nb - 1], [0, 3]], dtype=np.int64)      # one source copied twice
+    want_k = [k.cpu().view(torch.uint8).numpy().reshape(nb, -1).copy() for k in keys]
+    want_v = [v.cpu().view(torch.uint8).numpy().reshape(nb, -1).copy() for v in vals]
+    oracle_copy_blocks(want_k, want_v, mapping)
+    pa.copy_blocks(keys, vals, torch.from_numpy(mapping).to(dev))
+    torch.cuda.synchronize()
+    for k, v, wk, wv in zip(keys, vals, want_k, want_v):
+        assert np.array_equal(k.cpu().view(torch.uint8).numpy().reshape(nb, -1), wk)
+        assert np.array_equal(v.cpu().view(torch.uint8).numpy().reshape(nb, -1), wv)
+
+
+def test_copy_blocks_large_block_split_and_empty():
+    import torch
+    import attention_rs_b200 as pa
+    dev = torch.device("cuda:0")
+    shape = (5, 8, 128, 32)                                    # 64 KB blocks: the launcher splits a pair over several CTAs
+    k = torch.randn(shape, device=dev).to(torch.bfloat16)
+    v = torch.randn(shape, device=dev).to(torch.bfloat16)
+    k0, v0 = k.clone(), v.clone()
+    pa.copy_blocks([k], [v], torch.tensor([[1, 3]], device=dev, dtype=torch.int64))
+    torch.cuda.synchronize()
+    assert torch.equal(k[3].view(torch.int16), k0[1].view(torch.int16)) and torch.equal(v[3].view(torch.int16), v0[1].view(torch.int16))
+    for b in (0, 1, 2, 4):
+        assert torch.equal(k[b].view(torch.int16), k0[b].view(torch.int16))
+    pa.copy_blocks([k], [v], torch.zeros((0, 2), device=dev, dtype=torch.int64))   # no pairs: a no-op
+    torch.cuda.synchronize()
