@@ -1,6 +1,6 @@
 // Shared definitions of the sm_100a paged-attention library: dtype codes, status
 // codes, the device status word, and thin wrappers over the PTX this library
-// uses (mbarrier, 1-D bulk async copy, ldmatrix, warp-level MMA, FP8 convert).
+// uses (mbarrier, 1-D bulk async copy, ldmatrix, movmatrix, warp-level MMA, FP8 convert).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -90,10 +90,6 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
                : "r"(addr));
 }
 
-__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
-}
-
 // Transposes an 8x8 matrix of 16-bit elements held one row per lane quad (the MMA fragment layout).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t d;
@@ -124,34 +120,6 @@ __device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uin
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// D += A(16x32, row) * B(32x8, col), fp32 accumulate, FP8 E4M3 inputs (four bytes per register).
-__device__ __forceinline__ void mma16832_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Two fp32 values -> two FP8 E4M3 bytes (lo in bits 0-7, hi in bits 8-15), RN-even, saturating.
-__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
-// Splits two non-negative-or-signed fp32 values into FP8 "head" bytes and FP8 "tail" bytes with
-// head + tail ~= value to about 2^-8 relative: head = rn(value), tail = rn(value - head).
-__device__ __forceinline__ void split_e4m3x2(float lo, float hi, uint32_t& head, uint32_t& tail) {
-  head = f32x2_to_e4m3x2(lo, hi);
-  uint32_t back, val, res;
-  uint16_t t;
-  asm("{\n\t.reg .b16 h;\n\tcvt.u16.u32 h, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, h;\n\t}" : "=r"(back) : "r"(head));
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(val) : "f"(hi), "f"(lo));
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(res) : "r"(val), "r"(back));
-  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(t) : "r"(res));
-  tail = t;
 }
 
 // Two FP8 E4M3 bytes (low 16 bits of v) -> packed f16x2.  Exact.

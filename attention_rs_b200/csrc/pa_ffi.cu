@@ -127,6 +127,8 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
   if (a.head_size % (16 / kvsize) != 0)
     return fail(PA_ERR_UNSUPPORTED, "head_size %d is not a multiple of the key-cache chunk width %d", a.head_size, 16 / kvsize);
 
+  if (a.num_seqs > 65535)
+    return fail(PA_ERR_UNSUPPORTED, "num_seqs %d exceeds the 65535 sequences one launch takes (the reference's grid has the same limit)", a.num_seqs);
   DecodeParams p;
   p.out = a.out;
   p.exp_sums = a.exp_sums;

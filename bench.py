@@ -147,7 +147,11 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     w = workloads.decode_workload(args.config, num_seqs=args.num_seqs)
-    w.seed = w.seed + 1000 * rank           # every rank owns different heads of the wider model
+    if args.scaling == "strong" and world > 1:
+        # Fixed total problem: the configuration's kv heads (and their query heads, slopes, cache slices) are
+        # split over the ranks, as the multi-GPU configurations describe; block tables and lengths replicate.
+        w = w.shard(rank, world)
+    w.seed = w.seed + 1000 * rank           # every rank owns different heads
     t = workloads.device_tensors(w, dev)
     q, kc, vc, bt, cl = t["q"], t["key_cache"], t["value_cache"], t["block_tables"], t["context_lens"]
     slopes, k_scale, v_scale = t["alibi_slopes"], t["k_scale"], t["v_scale"]
@@ -280,7 +284,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": round(per_step_ms, 5), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": w.dtype if not fp8 else "fp8_e4m3 cache / bf16 query",
+            "scaling": args.scaling, "vs_baseline": None, "dtype": w.dtype if not fp8 else "fp8_e4m3 cache / bf16 query",
             "data": "synthetic", "config": describe(w, world, args.gather),
             "tokens_per_s": round(world * w.num_seqs / (per_step_ms * 1e-3), 1),
             "pct_of_8TBps_nominal_per_gpu": round(100.0 * per_gpu / NOMINAL_HBM_GBS, 2),
@@ -547,6 +551,9 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="shrink the batch (same shapes and length distribution); for profiler captures only")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: weak = every rank runs the configuration's shape (an N-times-wider model); strong = "
+                         "the configuration's kv heads are split over the ranks")
     ap.add_argument("--gather", action="store_true", help="all-gather the outputs inside the timed step (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline leg")
