@@ -144,6 +144,32 @@ def test_single_pass_cluster_sizes(dev, cluster, monkeypatch):
     check(run_ours(c, case_to_device(c, dev), "v1"), c.expected(), "bf16", what=f"cluster {cluster} d80 bs8")
 
 
+def _random_cases(n, seed):
+    rng = np.random.default_rng(seed)
+    for i in range(n):
+        dtype = str(rng.choice(["bf16", "f16"]))
+        hs = int(rng.choice([64, 80, 96, 112, 128, 192, 256]))
+        bs = int(rng.choice([8, 16, 32]))
+        kv = "fp8" if (rng.random() < 0.3 and hs % 32 == 0 and bs >= 16) else None
+        nkv = int(rng.integers(1, 4))
+        group = int(rng.choice([1, 2, 3, 4, 5, 8, 12, 16, 20]))
+        ns = int(rng.integers(1, 6))
+        ctx = [int(c) for c in rng.integers(0, int(rng.choice([40, 600, 2600])), size=ns)]
+        if max(ctx) == 0:
+            ctx[0] = 7
+        yield dict(ctx=ctx, nh=nkv * group, nkv=nkv, hs=hs, bs=bs, dtype=dtype, kv=kv, alibi=bool(rng.random() < 0.3),
+                   softcap=float(rng.choice([1.0, 1.0, 10.0, 50.0])), mode=str(rng.choice(["v1", "v2", "api"])), seed=1000 + i)
+
+
+@pytest.mark.parametrize("case", list(_random_cases(48, 2024)), ids=lambda c: f"{c['dtype']}-{c['kv']}-d{c['hs']}-bs{c['bs']}-g{c['nh'] // c['nkv']}-{c['mode']}")
+def test_random_shapes(dev, case):
+    """Seeded random walk over the template space: head sizes, block sizes, group sizes (one or two n-tiles of
+    heads, several CTAs per kv head), FP8 caches, ALiBi, soft-cap, empty and ragged contexts, all entry points."""
+    c = make_case(case["ctx"], case["nh"], case["nkv"], case["hs"], case["bs"], case["dtype"], case["kv"],
+                  seed=case["seed"], alibi=case["alibi"], softcapping=case["softcap"])
+    check(run_ours(c, case_to_device(c, dev), case["mode"]), c.expected(), case["dtype"], case["kv"], what=str(case))
+
+
 def test_legacy_symbols_match_ex(dev):
     c = make_case([33, 700, 64], 8, 2, 128, 16, "bf16", seed=51)
     d = case_to_device(c, dev)
