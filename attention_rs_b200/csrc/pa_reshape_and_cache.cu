@@ -124,23 +124,28 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
 
   for (int cs = row_lo; cs < row_hi; cs += SLICE) {
     const int cols = min(SLICE, row_hi - cs);         // a multiple of X, hence of VEC
-    // ---- stage the value rows of this pass's tokens
+    // ---- stage the value rows of this pass's tokens: one warp per token, one 16-byte vector per lane
+    // (a slice is at most 32 vectors wide), so no index arithmetic beyond adds
     const int vec_per_tok = cols / VEC;
-    for (int idx = tid; idx < ntok * vec_per_tok; idx += RC_THREADS) {
-      const int j = idx / vec_per_tok, v = idx % vec_per_tok;
-      if (s_blk[j] < 0) continue;
-      *reinterpret_cast<uint4*>(&s_val[j][v * VEC]) =
-          *reinterpret_cast<const uint4*>(value + (tok0 + j) * value_stride + cs + v * VEC);
-    }
-    // ---- keys: one 16-byte chunk of the cache per thread-iteration, flat over (token, chunk)
-    const int chunk_lo = cs / X, nchunk = cols / X;
+    const int warp = tid >> 5, lane = tid & 31;
 #pragma unroll 4
-    for (int idx = tid; idx < ntok * nchunk; idx += RC_THREADS) {
-      const int j = idx / nchunk, c = chunk_lo + idx % nchunk;
+    for (int j = warp; j < ntok; j += RC_THREADS / 32) {
+      if (s_blk[j] < 0 || lane >= vec_per_tok) continue;
+      *reinterpret_cast<uint4*>(&s_val[j][lane * VEC]) =
+          *reinterpret_cast<const uint4*>(value + (tok0 + j) * value_stride + cs + lane * VEC);
+    }
+    // ---- keys: one 16-byte chunk of the cache per lane, one warp per token
+#ifndef PA_DEBUG_RC_SKIP_K
+    const int chunk_lo = cs / X, nchunk = cols / X;   // nchunk <= 32
+    const int h_lo = chunk_lo / cph, ci_lo = chunk_lo % cph;
+#pragma unroll 4
+    for (int j = warp; j < ntok; j += RC_THREADS / 32) {
       const int64_t blk = s_blk[j];
-      if (blk < 0) continue;
-      const int h = c / cph, ci = c % cph;
-      const S* src = key + (tok0 + j) * key_stride + c * X;
+      if (blk < 0 || lane >= nchunk) continue;
+      // chunk chunk_lo + lane of the token: head h, chunk ci within the head (a slice spans at most a few heads)
+      int h = h_lo, ci = ci_lo + lane;
+      while (ci >= cph) { ci -= cph; ++h; }
+      const S* src = key + (tok0 + j) * key_stride + (chunk_lo + lane) * X;
       Pack<D, X> outv;
       if constexpr (!QUANT) {
         outv = *reinterpret_cast<const Pack<D, X>*>(src);
@@ -152,7 +157,11 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
       D* dst = key_cache + (((blk * num_heads + h) * cph + ci) * BS + s_off[j]) * X;
       *reinterpret_cast<Pack<D, X>*>(dst) = outv;
     }
+#endif
     __syncthreads();
+#ifdef PA_DEBUG_RC_SKIP_V
+    continue;
+#endif
 
     // ---- values out of shared memory.  A thread owns two adjacent rows of the cache.
     // tokens alone in their block: one element per row
@@ -192,13 +201,46 @@ reshape_and_cache_kernel(const S* __restrict__ key, const S* __restrict__ value,
           *reinterpret_cast<Pack<D, PIECE>*>(dst) = out0;
           *reinterpret_cast<Pack<D, PIECE>*>(dst + BS) = out1;
         } else {
+          // A ragged piece (a padding token inside it, or the edge of this CTA's tokens): aligned runs of four
+          // and of two present tokens still leave as one store each, the rest element by element.
+          auto ld = [&](int e) { return *reinterpret_cast<const Pack<S, 2>*>(&s_val[g_map[g][pc * PIECE + e]][r]); };
 #pragma unroll
-          for (int e = 0; e < PIECE; ++e)
-            if (sub & (1u << e)) {
-              const Pack<S, 2> in = *reinterpret_cast<const Pack<S, 2>*>(&s_val[g_map[g][pc * PIECE + e]][r]);
-              dst[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
-              dst[BS + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+          for (int q4 = 0; q4 < PIECE; q4 += 4) {
+            const unsigned quad = (sub >> q4) & 0xfu;
+            if (quad == 0u) continue;
+            if (quad == 0xfu) {
+              Pack<D, 4> o0, o1;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const Pack<S, 2> in = ld(q4 + e);
+                o0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+                o1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+              }
+              *reinterpret_cast<Pack<D, 4>*>(dst + q4) = o0;
+              *reinterpret_cast<Pack<D, 4>*>(dst + BS + q4) = o1;
+              continue;
             }
+#pragma unroll
+            for (int p2 = 0; p2 < 4; p2 += 2) {
+              const unsigned pair = (quad >> p2) & 0x3u;
+              if (pair == 0x3u) {
+                Pack<D, 2> o0, o1;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const Pack<S, 2> in = ld(q4 + p2 + e);
+                  o0.v[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+                  o1.v[e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+                }
+                *reinterpret_cast<Pack<D, 2>*>(dst + q4 + p2) = o0;
+                *reinterpret_cast<Pack<D, 2>*>(dst + BS + q4 + p2) = o1;
+              } else if (pair != 0u) {
+                const int e = q4 + p2 + (pair >> 1);
+                const Pack<S, 2> in = ld(e);
+                dst[e] = convert_elem<S, D, QUANT>(in.v[0], v_scale);
+                dst[BS + e] = convert_elem<S, D, QUANT>(in.v[1], v_scale);
+              }
+            }
+          }
         }
       }
     }
