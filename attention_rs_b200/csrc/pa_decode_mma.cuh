@@ -744,13 +744,24 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
   float a[PER_LANE];
 #pragma unroll
   for (int k = 0; k < PER_LANE; ++k) a[k] = 0.f;
-  for (int j = warp; j < nparts; j += NWARP) {
-    const float w = wgt[j];
+  // Four partitions per iteration: their loads are independent, so four rows are in flight per warp.
+  for (int j0 = warp; j0 < nparts; j0 += 4 * NWARP) {
+    float w[4];
+    T v[4][PER_LANE];
 #pragma unroll
-    for (int k = 0; k < PER_LANE; ++k) {
-      const int d = lane + k * 32;
-      if (d < HEAD && w != 0.f) a[k] += w * to_f32<T>(tp[static_cast<int64_t>(j) * HEAD + d]);
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u * NWARP;
+      w[u] = j < nparts ? wgt[j] : 0.f;
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) {
+        const int d = lane + k * 32;
+        v[u][k] = (d < HEAD && w[u] != 0.f) ? tp[static_cast<int64_t>(j) * HEAD + d] : from_f32<T>(0.f);
+      }
     }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int k = 0; k < PER_LANE; ++k) a[k] += w[u] * to_f32<T>(v[u][k]);
   }
 #pragma unroll
   for (int k = 0; k < PER_LANE; ++k) {

@@ -177,8 +177,11 @@ int launch_paged_attention(const AttnArgs& a, cudaStream_t stream) {
   if (a.partitioned) {
     const long part_bytes = 2L * PA_PARTITION_SIZE * a.head_size * kvsize;
     const long ctas = static_cast<long>(a.num_seqs) * a.num_kv_heads * ((p.group + 15) / 16) * p.max_parts;
+    // Narrow partitions (FP8, small heads: under 192 KB) gain much more from folding than wide ones lose to a
+    // coarser grid, so they fold down to about two waves of CTAs; wide ones only while the grid stays large.
+    const long min_ctas = part_bytes < 192 * 1024 ? 1000 : 6000;
     while (p.parts_per_cta < 4 && part_bytes * p.parts_per_cta < 512 * 1024 && p.parts_per_cta * 2 <= p.max_parts &&
-           ctas / (p.parts_per_cta * 2) >= 6000)
+           ctas / (p.parts_per_cta * 2) >= min_ctas)
       p.parts_per_cta *= 2;
     if (const char* e = getenv("PA_V2_PARTS_PER_CTA")) {   // tuning override
       const int v = atoi(e);

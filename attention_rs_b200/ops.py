@@ -104,18 +104,30 @@ def dtype_code(t: torch.Tensor) -> int:
     raise PagedAttentionError(f"dtype {t.dtype} is not supported")
 
 
+_DESC_CACHE: dict = {}
+
+
 def _desc(t: Optional[torch.Tensor]) -> Optional[_Tensor]:
+    """Descriptor of a tensor for the C ABI.  A serving loop passes the same caches, tables and staging
+    buffers every step, so descriptors are memoised on (address, dtype, shape, strides)."""
     if t is None:
         return None
+    key = (t.data_ptr(), t.dtype, tuple(t.shape), t.stride())
+    d = _DESC_CACHE.get(key)
+    if d is not None:
+        return d
     if t.dim() > 5:
         raise PagedAttentionError(f"tensor of rank {t.dim()} is not supported")
     d = _Tensor()
-    d.data = t.data_ptr()
+    d.data = key[0]
     d.dtype = dtype_code(t)
     d.rank = t.dim()
     for i in range(t.dim()):
-        d.shape[i] = t.shape[i]
-        d.stride[i] = t.stride(i)
+        d.shape[i] = key[2][i]
+        d.stride[i] = key[3][i]
+    if len(_DESC_CACHE) >= 512:
+        _DESC_CACHE.clear()
+    _DESC_CACHE[key] = d
     return d
 
 
