@@ -19,6 +19,7 @@ from .ops import (  # noqa: F401
     paged_attention,
     paged_attention_v1,
     paged_attention_v2,
+    prefill_attention,
     reshape_and_cache,
     uses_partitions,
     workspace_bytes,

@@ -1,0 +1,289 @@
+// Causal self-attention over packed variable-length prompts (the prefill that precedes decode).
+//
+// What the reference's layer does for a prompt (src/lib.rs:87-213): with its flash-attn feature one call of
+// flash_attn_varlen (causal, optional soft-cap, src/lib.rs:103-125), otherwise per sequence and per 1024 query
+// rows `matmul * scale -> tanh soft-cap -> + causal mask -> softmax in f32 -> matmul` (src/lib.rs:178-203),
+// with kv heads repeated for grouped queries (src/lib.rs:131-143).  This file computes the same function in
+// one kernel, tile by tile with an online softmax, for tensors packed as [total_tokens, heads, head_size]
+// and sequence boundaries given by cu_seqlens.
+//
+// One CTA = 64 query rows of one (sequence, head), four warps of 16 rows.  K / V tiles of 64 tokens stream
+// through a double-buffered shared-memory ring (cp.async, 16 bytes per thread, XOR-swizzled so that ldmatrix is
+// conflict-free); S = Q K^T and O += P V run on warp-level m16n8k16 MMAs with P taken straight from the S
+// accumulators.  Later query tiles do more work (causal), so tiles are issued longest first.
+// This is a dense contraction, bounded by the tensor pipe, unlike the rest of the library.
+#include "pa_common.cuh"
+#include "pa_launch.h"
+
+namespace pa {
+namespace {
+
+constexpr int PF_BM = 64;   // query rows per CTA
+constexpr int PF_BN = 64;   // kv tokens per tile
+constexpr int PF_THREADS = 128;
+
+struct PrefillParams {
+  void* out;
+  const void* q;
+  const void* k;
+  const void* v;
+  const uint32_t* cu_seqlens;   // [num_seqs + 1]
+  const float* alibi_slopes;    // may be null
+  int64_t q_stride, k_stride, v_stride, o_stride;   // token strides, elements
+  int num_heads, num_kv_heads, max_seqlen;
+  float scale, softcap;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // zero-fill when the row lies outside the sequence
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+// Byte offset of 16-byte chunk c of row r in a tile whose rows are HEAD 16-bit elements, XOR-swizzled.
+template <int HEAD>
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return static_cast<uint32_t>(r * (HEAD * 2) + ((c ^ (r & 7)) << 4));
+}
+
+template <typename T, int HEAD>
+__global__ void __launch_bounds__(PF_THREADS)
+prefill_attention_kernel(const PrefillParams p) {
+  constexpr int CH = HEAD / 8;        // 16-byte chunks per row
+  constexpr int KS = HEAD / 16;       // k-steps of S = Q K^T
+  constexpr int NT_S = PF_BN / 8;     // n-tiles of S
+  constexpr int NT_O = HEAD / 8;      // n-tiles of O
+  constexpr int TILE_BYTES = PF_BN * HEAD * 2;
+  static_assert(HEAD % 64 == 0, "the swizzle assumes rows of whole 128-byte groups");
+
+  const int seq = blockIdx.y, head = blockIdx.z;
+  const int tok_lo = static_cast<int>(p.cu_seqlens[seq]), tok_hi = static_cast<int>(p.cu_seqlens[seq + 1]);
+  const int len = tok_hi - tok_lo;
+  const int ntiles = (len + PF_BM - 1) / PF_BM;
+  const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // heaviest (last) tiles first
+  if (qt >= ntiles) return;
+  const int kvh = head / (p.num_heads / p.num_kv_heads);
+  const int q0 = qt * PF_BM;                       // first query row of this CTA, within the sequence
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gi = lane >> 2, qi = lane & 3;
+
+  extern __shared__ __align__(128) unsigned char pf_smem[];
+  const uint32_t sQ = smem_addr(pf_smem);                       // [64][HEAD]
+  const uint32_t sK = sQ + PF_BM * HEAD * 2;                    // 2 x [64][HEAD]
+  const uint32_t sV = sK + 2 * TILE_BYTES;                      // 2 x [64][HEAD]
+
+  const T* qg = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(tok_lo + q0) * p.q_stride + head * HEAD;
+  const T* kg = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(tok_lo) * p.k_stride + kvh * HEAD;
+  const T* vg = reinterpret_cast<const T*>(p.v) + static_cast<int64_t>(tok_lo) * p.v_stride + kvh * HEAD;
+
+  // ---- loads: 64 rows x CH chunks, 128 threads
+  auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int row0, int rows_valid) {
+#pragma unroll
+    for (int i = threadIdx.x; i < PF_BN * CH; i += PF_THREADS) {
+      const int r = i / CH, c = i % CH;
+      cp_async16(dst + swz<HEAD>(r, c), src + static_cast<int64_t>(row0 + r) * stride + c * 8, r < rows_valid);
+    }
+  };
+  load_tile(sQ, qg, p.q_stride, 0, len - q0);
+  const int n_kv_tiles = qt + 1;                   // causal: kv tiles 0..qt
+  load_tile(sK, kg, p.k_stride, 0, len);
+  load_tile(sV, vg, p.v_stride, 0, len);
+  cp_async_commit();
+
+  const float slope = p.alibi_slopes ? p.alibi_slopes[head] : 0.f;
+  const bool capped = p.softcap != 1.0f;
+  const float scale_log2 = p.scale * LOG2E;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  uint32_t qa[KS][4];
+
+  for (int j = 0; j < n_kv_tiles; ++j) {
+    const int buf = j & 1;
+    if (j + 1 < n_kv_tiles) {                      // prefetch the next tile into the other buffer
+      load_tile(sK + (buf ^ 1) * TILE_BYTES, kg, p.k_stride, (j + 1) * PF_BN, len - (j + 1) * PF_BN);
+      load_tile(sV + (buf ^ 1) * TILE_BYTES, vg, p.v_stride, (j + 1) * PF_BN, len - (j + 1) * PF_BN);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (j == 0) {                                  // this warp's 16 query rows as A fragments, kept in registers
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(sQ + swz<HEAD>(r, c), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
+      }
+    }
+    const uint32_t kt = sK + buf * TILE_BYTES, vt = sV + buf * TILE_BYTES;
+
+    // ---- S = Q K^T (16 x 64 per warp)
+    float s[NT_S][4];
+#pragma unroll
+    for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+      for (int n = 0; n < NT_S; n += 2) {
+        const int r = n * 8 + (lane & 7) + (lane >> 4) * 8, c = ks * 2 + ((lane >> 3) & 1);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(kt + swz<HEAD>(r, c), b0, b1, b2, b3);
+        mma16816<T>(s[n], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        mma16816<T>(s[n + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+      }
+    }
+
+    // ---- logits (log2 domain), causal / length mask, online softmax for rows gi and gi + 8
+    const int row0 = q0 + warp * 16 + gi;          // query position within the sequence
+    const bool diag = (j == n_kv_tiles - 1);
+#pragma unroll
+    for (int n = 0; n < NT_S; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = j * PF_BN + n * 8 + 2 * qi + (e & 1);   // key position
+        const int row = row0 + (e >> 1) * 8;
+        float x = s[n][e];
+        if (capped) x = tanh_approx(x * p.scale / p.softcap) * p.softcap * LOG2E;
+        else x *= scale_log2;
+        if (slope != 0.f) x += slope * LOG2E * static_cast<float>(col - row);
+        if (col >= len || (diag && col > row)) x = -INFINITY;
+        s[n][e] = x;
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m[h], mx);
+      const float base = mn == -INFINITY ? 0.f : mn;   // a row past the sequence end sees no key at all
+      corr[h] = exp2_approx(m[h] - base);
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) {
+        s[n][2 * h] = exp2_approx(s[n][2 * h] - base);
+        s[n][2 * h + 1] = exp2_approx(s[n][2 * h + 1] - base);
+        sum += s[n][2 * h] + s[n][2 * h + 1];
+      }
+      l[h] = l[h] * corr[h] + sum;
+      m[h] = mn;
+    }
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < PF_BN / 16; ++kk) {
+      const uint32_t a0 = pack2<T>(s[2 * kk][0], s[2 * kk][1]), a1 = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int n = 0; n < NT_O; n += 2) {
+        const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = n + (lane >> 4);
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vt + swz<HEAD>(r, c), b0, b1, b2, b3);
+        mma16816<T>(o[n], a0, a1, a2, a3, b0, b1);
+        mma16816<T>(o[n + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();   // the buffer just read is the target of the next iteration's prefetch
+  }
+
+  // ---- normalise and store
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+  }
+  T* og = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + q0) * p.o_stride + head * HEAD;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + gi + h * 8;
+    if (q0 + r < len) {
+      const float inv = 1.0f / l[h];
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n)
+        *reinterpret_cast<uint32_t*>(og + static_cast<int64_t>(r) * p.o_stride + n * 8 + 2 * qi) =
+            pack2<T>(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
+  }
+}
+
+template <typename T, int HEAD>
+int launch_prefill(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
+  auto kernel = prefill_attention_kernel<T, HEAD>;
+  constexpr int smem = (PF_BM + 4 * PF_BN) * HEAD * 2;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return PA_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return PA_ERR_CUDA;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid((p.max_seqlen + PF_BM - 1) / PF_BM, num_seqs, p.num_heads);
+  kernel<<<grid, PF_THREADS, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+}  // namespace
+}  // namespace pa
+
+extern "C" int paged_prefill_attention(void* out, const void* query, const void* key, const void* value,
+                                       const uint32_t* cu_seqlens, int32_t num_seqs, int32_t max_seqlen,
+                                       int32_t num_heads, int32_t num_kv_heads, int32_t head_size, int32_t q_stride,
+                                       int32_t k_stride, int32_t v_stride, int32_t out_stride, float scale,
+                                       float softcapping, const float* alibi_slopes, uint32_t dtype, int64_t stream) {
+  using namespace pa;
+  if (num_seqs == 0 || max_seqlen == 0) return PA_OK;
+  if (!out || !query || !key || !value || !cu_seqlens) return fail(PA_ERR_INVALID_ARGUMENT, "null pointer passed to paged_prefill_attention");
+  if (num_seqs < 0 || num_seqs > 65535 || max_seqlen < 0 || num_heads <= 0 || num_heads > 65535 || num_kv_heads <= 0 ||
+      num_heads % num_kv_heads != 0)
+    return fail(PA_ERR_INVALID_ARGUMENT, "bad sizes passed to paged_prefill_attention");
+  if (dtype != DT_F16 && dtype != DT_BF16) return fail(PA_ERR_UNSUPPORTED, "prefill attention takes f16 or bf16 tensors");
+  const bool aligned = ((reinterpret_cast<uintptr_t>(query) | reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) % 16 == 0) &&
+                       reinterpret_cast<uintptr_t>(out) % 4 == 0 && q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 &&
+                       out_stride % 2 == 0;
+  if (!aligned) return fail(PA_ERR_UNSUPPORTED, "prefill attention needs 16-byte aligned rows");
+  PrefillParams p;
+  p.out = out;
+  p.q = query;
+  p.k = key;
+  p.v = value;
+  p.cu_seqlens = cu_seqlens;
+  p.alibi_slopes = alibi_slopes;
+  p.q_stride = q_stride;
+  p.k_stride = k_stride;
+  p.v_stride = v_stride;
+  p.o_stride = out_stride;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.max_seqlen = max_seqlen;
+  p.scale = scale;
+  p.softcap = softcapping;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc = PA_ERR_UNSUPPORTED;
+  if (dtype == DT_BF16) {
+    if (head_size == 64) rc = launch_prefill<__nv_bfloat16, 64>(p, num_seqs, s);
+    else if (head_size == 128) rc = launch_prefill<__nv_bfloat16, 128>(p, num_seqs, s);
+    else if (head_size == 256) rc = launch_prefill<__nv_bfloat16, 256>(p, num_seqs, s);
+  } else {
+    if (head_size == 64) rc = launch_prefill<__half, 64>(p, num_seqs, s);
+    else if (head_size == 128) rc = launch_prefill<__half, 128>(p, num_seqs, s);
+    else if (head_size == 256) rc = launch_prefill<__half, 256>(p, num_seqs, s);
+  }
+  if (rc == PA_ERR_UNSUPPORTED) return fail(rc, "prefill attention supports head sizes 64, 128 and 256 (got %d)", head_size);
+  return rc == PA_OK ? rc : fail(rc, "prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+}

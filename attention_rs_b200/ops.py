@@ -73,6 +73,8 @@ def load_library() -> ctypes.CDLL:
     L.paged_decode_step_v1.argtypes = [vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
     L.paged_decode_step_v2.restype = ctypes.c_int
     L.paged_decode_step_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
+    L.paged_prefill_attention.restype = ctypes.c_int
+    L.paged_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp, u32, i64]
     L.pa_copy_blocks.restype = ctypes.c_int
     L.pa_copy_blocks.argtypes = [vp, vp, vp, i32, i32, i32, i32, i64]
     L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t
@@ -251,6 +253,33 @@ def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.T
         rc = L.pa_reshape_and_cache(_ref(_desc(key)), _ref(_desc(value)), _ref(_desc(key_cache)), _ref(_desc(value_cache)),
                                     _ref(_desc(slot_mapping)), float(k_scale), float(v_scale), stream)
     _check(rc)
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
+                      softmax_scale: float, softcapping: float = 1.0, alibi_slopes: Optional[torch.Tensor] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal self-attention over packed prompts (the prefill of the reference's layer, src/lib.rs:87-213).
+    q [tokens, heads, d], k / v [tokens, kv_heads, d] (f16 / bf16, rows may be strided views of a fused tensor),
+    cu_seqlens int32 [num_seqs + 1] on the device."""
+    L = load_library()
+    dev = _require_cuda(q, k, v, cu_seqlens, alibi_slopes, out)
+    if q.dim() != 3 or k.dim() != 3 or v.shape != k.shape or q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
+        raise PagedAttentionError("prefill attention expects q [tokens, heads, d] and k, v [tokens, kv_heads, d]")
+    for t in (q, k, v):
+        if t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+            raise PagedAttentionError("q, k and v must be contiguous in their last two dimensions")
+    if dtype_code(cu_seqlens) != U32 or cu_seqlens.dim() != 1 or not cu_seqlens.is_contiguous():
+        raise PagedAttentionError("cu_seqlens must be a contiguous int32 tensor [num_seqs + 1]")
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        rc = L.paged_prefill_attention(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(),
+                                       cu_seqlens.shape[0] - 1, int(max_seqlen), q.shape[1], k.shape[1], q.shape[2],
+                                       q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(softmax_scale),
+                                       float(softcapping), None if alibi_slopes is None else alibi_slopes.data_ptr(),
+                                       dtype_code(q), torch.cuda.current_stream(dev).cuda_stream)
+    _check(rc)
+    return out
 
 
 def copy_blocks(key_caches, value_caches, block_mapping: torch.Tensor) -> None:

@@ -525,6 +525,68 @@ def run_scatter(args):
     emit(line)
 
 
+def run_prefill(args):
+    """Prefill (row F3): causal self-attention over 16 packed prompts of 2048 tokens, 32 q / 8 kv heads, d128,
+    bf16.  Metric: useful tensor throughput, 4 * head_size flop per (query, key) pair under the causal mask."""
+    import torch
+    import attention_rs_b200 as pa
+    rank, world, local = dist_env()
+    if world > 1:
+        raise SystemExit("--config 6 is a single-GPU measurement")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ns, seqlen, nh, nkv, hs = 16, 2048, 32, 8, 128
+    g = torch.Generator(device=dev)
+    g.manual_seed(20246)
+    qkv = torch.randn((ns * seqlen, nh + 2 * nkv, hs), generator=g, device=dev).to(torch.bfloat16)
+    q, k, v = qkv[:, :nh], qkv[:, nh:nh + nkv], qkv[:, nh + nkv:]           # views of a fused projection output
+    cu = torch.arange(0, (ns + 1) * seqlen, seqlen, dtype=torch.int32, device=dev)
+    scale = hs ** -0.5
+    flops = ns * nh * 4.0 * hs * (seqlen * (seqlen + 1) / 2)
+    out = torch.empty((ns * seqlen, nh, hs), dtype=torch.bfloat16, device=dev)
+    sampler = ClockSampler(local).start()
+
+    def timed(fn, steps):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    steps = min(args.steps, 200)
+    ms = timed(lambda: pa.prefill_attention(q, k, v, cu, seqlen, scale, out=out), steps)
+    line = {"metric": "prefill_attention_tensor_throughput", "value": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"prefill: {ns} prompts x {seqlen} tokens, {nh} q / {nkv} kv heads, head_dim {hs}, causal, "
+                                   "q / k / v as strided views of one fused tensor",
+                       "l2": "the step reads 100 MB of q / k / v and writes 134 MB; tensor-bound"},
+            "gpu_launches": steps, "e2e": None}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, kind = float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+    line["roofline"] = {"bound": "tensor", "achieved": line["value"], "peak": peak, "unit": "TFLOP/s",
+                        "frac": round(line["value"] / peak, 4), "peak_kind": f"of {kind}", "traffic": None,
+                        "algorithmic_flops_per_launch": flops}
+    if args.impl == "reference":
+        # Context: the FlashAttention-2 library kernels, which is what the reference's flash-attn feature wraps.
+        try:
+            from flash_attn import flash_attn_varlen_func
+            rms = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, seqlen, seqlen, softmax_scale=scale, causal=True), steps)
+            line["flash_attn_library"] = {"ms_per_step": round(rms, 5), "TFLOPs": round(flops / rms / 1e9, 1)}
+        except Exception as exc:
+            line["flash_attn_library"] = {"unavailable": repr(exc)[:200]}
+    line["clocks"] = sampler.stop()
+    emit(line)
+
+
 _RESULT_FD = None
 
 
@@ -554,7 +616,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5, 6],
+                    help="1, 2, 4, 5: decode workloads; 3: reshape_and_cache; 6: prefill attention")
     ap.add_argument("--num-seqs", type=int, default=None,
                     help="shrink the batch (same shapes and length distribution); for profiler captures only")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
@@ -565,7 +628,9 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the cpu_baseline leg")
     ap.add_argument("--ref-budget", type=float, default=90.0, help="seconds for all steps of --impl reference")
     args = ap.parse_args()
-    if args.config == 3:
+    if args.config == 6:
+        run_prefill(args)
+    elif args.config == 3:
         run_scatter(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -157,6 +157,20 @@ int paged_decode_step_v2(void* out, float* exp_sums, float* max_logits, void* tm
                          const float* alibi_slopes, uint32_t kv_cache_dtype, float k_scale, float v_scale,
                          int64_t stream);
 
+/* Prefill: causal self-attention over packed variable-length prompts, the step that precedes decode in the
+ * reference's layer (src/lib.rs:87-213: flash_attn_varlen with causal = true under its flash-attn feature,
+ * else per-sequence matmul / soft-cap / causal mask / f32 softmax / matmul, with kv heads repeated for grouped
+ * queries).  query / out: [total_tokens, num_heads, head_size]; key / value: [total_tokens, num_kv_heads,
+ * head_size]; token strides q_stride / k_stride / v_stride / out_stride in elements; cu_seqlens: u32
+ * [num_seqs + 1] prefix sums of the prompt lengths (device memory); max_seqlen: the longest prompt.
+ * f16 / bf16, head_size 64 / 128 / 256.  alibi_slopes may be NULL; softcapping == 1.0 disables the soft-cap.
+ * Writing the prompt's keys and values into the paged cache stays a call of call_reshape_and_cache. */
+int paged_prefill_attention(void* out, const void* query, const void* key, const void* value,
+                            const uint32_t* cu_seqlens, int32_t num_seqs, int32_t max_seqlen, int32_t num_heads,
+                            int32_t num_kv_heads, int32_t head_size, int32_t q_stride, int32_t k_stride,
+                            int32_t v_stride, int32_t out_stride, float scale, float softcapping,
+                            const float* alibi_slopes, uint32_t dtype, int64_t stream);
+
 /* copy_blocks: for every layer and every (source, destination) pair, copies one whole KV block inside the key
  * cache and inside the value cache.  Host launcher for the reference's copy_blocks kernels
  * (src/kernels/src/copy_blocks_kernel.cu:4-82), which the reference exports only as `extern "C" __global__`

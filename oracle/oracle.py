@@ -58,6 +58,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_paged_attention.argtypes = attn + [i32, i32]
         L.oracle_paged_attention_naive_f32.restype = ctypes.c_int
         L.oracle_paged_attention_naive_f32.argtypes = attn
+        L.oracle_prefill_attention.restype = ctypes.c_int
+        L.oracle_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int64, u32, f32, f32, vp]
         _lib = L
     return _lib
 
@@ -157,6 +160,40 @@ def paged_attention(query, key_cache, value_cache, block_tables, context_lens, s
         rc = lib().oracle_paged_attention(*args, partition_size, 1 if reference_literal_alibi else 0)
     if rc != 0:
         raise RuntimeError(f"oracle_paged_attention failed: {rc}")
+    return out
+
+
+def prefill_attention(q, k, v, cu_seqlens, scale, dtype, softcapping=1.0, alibi_slopes=None):
+    """fp32 [tokens, heads, head_size]: causal self-attention over packed prompts (storage arrays in)."""
+    nt, nh, hs = q.shape
+    nkv = k.shape[1]
+    cu = np.ascontiguousarray(cu_seqlens, dtype=np.uint32)
+    out = np.zeros((nt, nh, hs), dtype=np.float32)
+    sl = None if alibi_slopes is None else np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+    rc = lib().oracle_prefill_attention(_ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(cu), len(cu) - 1, nh, nkv, hs,
+                                        q.strides[0] // q.itemsize, k.strides[0] // k.itemsize,
+                                        v.strides[0] // v.itemsize, dtype, scale, softcapping, _ptr(sl))
+    if rc != 0:
+        raise RuntimeError(f"oracle_prefill_attention failed: {rc}")
+    return out
+
+
+def numpy_prefill_attention(q, k, v, cu_seqlens, scale, softcapping=1.0):
+    """fp64 twin of prefill_attention on fp32-decoded inputs; tiny shapes only."""
+    nt, nh, hs = q.shape
+    group = nh // k.shape[1]
+    out = np.zeros((nt, nh, hs), dtype=np.float64)
+    for s in range(len(cu_seqlens) - 1):
+        lo, hi = int(cu_seqlens[s]), int(cu_seqlens[s + 1])
+        n = hi - lo
+        mask = np.tril(np.ones((n, n), dtype=bool))
+        for h in range(nh):
+            logits = (q[lo:hi, h].astype(np.float64) @ k[lo:hi, h // group].astype(np.float64).T) * scale
+            if softcapping != 1.0:
+                logits = np.tanh(logits / softcapping) * softcapping
+            logits = np.where(mask, logits, -np.inf)
+            p = np.exp(logits - logits.max(axis=1, keepdims=True))
+            out[lo:hi, h] = (p / p.sum(axis=1, keepdims=True)) @ v[lo:hi, h // group].astype(np.float64)
     return out
 
 

@@ -415,3 +415,57 @@ int oracle_paged_attention_naive_f32(float* out, const void* query, const void* 
   }
   return 0;
 }
+
+/* ---------------------------------------------------------------- prefill attention */
+
+/*
+ * Causal self-attention over packed prompts: the function the reference's layer computes for a prefill
+ * (src/lib.rs:145-213 without its flash-attn feature: per sequence, logits = q k^T * scale, optional
+ * tanh soft-cap (:187-189), + causal mask (:191-195), softmax in f32 (:198-200), times v; kv heads repeated
+ * for grouped queries, :131-143; with the feature, flash_attn_varlen with causal = true, :103-125).
+ * q / k / v: [total_tokens, heads, head_size] with token strides in elements; cu_seqlens [num_seqs + 1].
+ * out: fp32 [total_tokens, num_heads, head_size].  The reference's own code for this function is Rust on
+ * candle tensors and cannot run where this oracle is tested: PARITY UNPINNED for this function.
+ */
+int oracle_prefill_attention(float* out, const void* q, const void* k, const void* v, const uint32_t* cu_seqlens,
+                             int32_t num_seqs, int32_t num_heads, int32_t num_kv_heads, int32_t head_size,
+                             int64_t q_stride, int64_t k_stride, int64_t v_stride, uint32_t dtype, float scale,
+                             float softcapping, const float* alibi_slopes) {
+  if (elem_size((int)dtype) == 0 || dtype == DT_FP8_E4M3) return -1;
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0) return -2;
+  const int group = num_heads / num_kv_heads;
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+  for (int s = 0; s < num_seqs; ++s) {
+    for (int h = 0; h < num_heads; ++h) {
+      const int lo = (int)cu_seqlens[s], hi = (int)cu_seqlens[s + 1];
+      const int kvh = h / group;
+      const float slope = alibi_slopes ? alibi_slopes[h] : 0.f;
+      double* logits = (double*)malloc(sizeof(double) * (size_t)(hi - lo + 1));
+      for (int r = lo; r < hi; ++r) {
+        double mx = -INFINITY;
+        for (int c = lo; c <= r; ++c) {
+          double dot = 0.0;
+          for (int d = 0; d < head_size; ++d)
+            dot += (double)load_elem(q, (int64_t)r * q_stride + (int64_t)h * head_size + d, (int)dtype) *
+                   (double)load_elem(k, (int64_t)c * k_stride + (int64_t)kvh * head_size + d, (int)dtype);
+          float x = scale * (float)dot;
+          if (softcapping != 1.0f) x = tanhf(x / softcapping) * softcapping;
+          x += slope * (float)(c - r);
+          logits[c - lo] = x;
+          if (x > mx) mx = x;
+        }
+        double sum = 0.0;
+        for (int c = lo; c <= r; ++c) { logits[c - lo] = exp(logits[c - lo] - mx); sum += logits[c - lo]; }
+        float* o = out + ((int64_t)r * num_heads + h) * head_size;
+        for (int d = 0; d < head_size; ++d) {
+          double acc = 0.0;
+          for (int c = lo; c <= r; ++c)
+            acc += logits[c - lo] * (double)load_elem(v, (int64_t)c * v_stride + (int64_t)kvh * head_size + d, (int)dtype);
+          o[d] = (float)(acc / sum);
+        }
+      }
+      free(logits);
+    }
+  }
+  return 0;
+}

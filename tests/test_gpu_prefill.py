@@ -1,0 +1,63 @@
+"""Prefill (causal varlen self-attention) through the C ABI against the CPU oracle."""
+import math
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.helpers import DT, from_torch_f32, to_torch, tolerances
+
+pytestmark = pytest.mark.gpu
+
+
+def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0):
+    import torch
+    import attention_rs_b200 as pa
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(seed)
+    dt = DT[dtype]
+    nt = int(sum(lens))
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    q = O.to_storage(rng.standard_normal((nt, nh + fused_pad, hs), dtype=np.float32), dt)
+    k = O.to_storage(rng.standard_normal((nt, nkv + fused_pad, hs), dtype=np.float32), dt)
+    v = O.to_storage(rng.standard_normal((nt, nkv + fused_pad, hs), dtype=np.float32), dt)
+    slopes = np.array([2.0 ** (-8.0 * (i + 1) / nh) for i in range(nh)], dtype=np.float32) if alibi else None
+    scale = 1.0 / math.sqrt(hs)
+    want = O.prefill_attention(q[:, :nh], k[:, :nkv], v[:, :nkv], cu, scale, dt, softcap, slopes)
+    tq, tk, tv = to_torch(q, dt, dev)[:, :nh], to_torch(k, dt, dev)[:, :nkv], to_torch(v, dt, dev)[:, :nkv]
+    got = pa.prefill_attention(tq, tk, tv, torch.from_numpy(cu.astype(np.int32)).to(dev), int(max(lens)), scale, softcap,
+                               None if slopes is None else torch.from_numpy(slopes).to(dev))
+    torch.cuda.synchronize()
+    got = from_torch_f32(got)
+    assert not np.isnan(got).any()
+    mx, mean = tolerances(dtype)
+    err = np.abs(got - want)
+    assert err.max() <= mx and err.mean() <= mean, f"max {err.max():.3e} mean {err.mean():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("hs", [64, 128, 256])
+def test_prefill_lengths_around_tile_edges(dtype, hs):
+    run([1, 63, 64, 65, 127, 129, 200], 4, 2, hs, dtype, seed=hs)
+
+
+def test_prefill_variants():
+    run([300, 5], 8, 8, 128, "bf16", seed=1)                       # MHA
+    run([90, 260], 8, 1, 128, "f16", seed=2)                        # MQA
+    run([150, 77], 4, 2, 128, "bf16", softcap=30.0, seed=3)
+    run([150, 77], 4, 2, 64, "f16", alibi=True, seed=4)
+    run([150, 77], 4, 2, 128, "bf16", seed=5, fused_pad=3)          # rows sliced out of wider tensors
+    run([700], 2, 1, 128, "bf16", seed=6)                           # many kv tiles
+
+
+def test_prefill_rejects_unsupported():
+    import torch
+    import attention_rs_b200 as pa
+    dev = torch.device("cuda:0")
+    q = torch.zeros((4, 2, 80), dtype=torch.bfloat16, device=dev)
+    cu = torch.tensor([0, 4], dtype=torch.int32, device=dev)
+    with pytest.raises(pa.PagedAttentionError, match="head sizes 64, 128 and 256"):
+        pa.prefill_attention(q, q, q, cu, 4, 0.1)
+    q32 = torch.zeros((4, 2, 64), dtype=torch.float32, device=dev)
+    with pytest.raises(pa.PagedAttentionError, match="f16 or bf16"):
+        pa.prefill_attention(q32, q32, q32, cu, 4, 0.1)

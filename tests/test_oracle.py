@@ -176,3 +176,19 @@ def test_oracle_against_reference_kernel_outputs(path):
         ref = O.from_storage(g[name], dt)
         err = np.abs(got - ref)
         assert err.max() <= max_tol and err.mean() <= mean_tol, f"{name}: max {err.max():.3e} mean {err.mean():.3e}"
+
+
+def test_prefill_oracle_matches_numpy_twin():
+    rng = np.random.default_rng(21)
+    lens = [1, 17, 40]
+    nt = sum(lens)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    q = O.to_storage(rng.standard_normal((nt, 4, 32), dtype=np.float32), O.BF16)
+    k = O.to_storage(rng.standard_normal((nt, 2, 32), dtype=np.float32), O.BF16)
+    v = O.to_storage(rng.standard_normal((nt, 2, 32), dtype=np.float32), O.BF16)
+    got = O.prefill_attention(q, k, v, cu, 0.2, O.BF16, softcapping=15.0)
+    want = O.numpy_prefill_attention(O.from_storage(q, O.BF16), O.from_storage(k, O.BF16), O.from_storage(v, O.BF16), cu,
+                                     0.2, softcapping=15.0)
+    assert np.abs(got - want).max() < 2e-6
+    # the last row of a sequence attends over the whole sequence; the first only over itself
+    assert np.allclose(got[0], np.repeat(O.from_storage(v, O.BF16)[0], 2, axis=0), atol=1e-6)
