@@ -7,32 +7,24 @@
 // one kernel, tile by tile with an online softmax, for tensors packed as [total_tokens, heads, head_size]
 // and sequence boundaries given by cu_seqlens.
 //
-// One CTA = 64 query rows of one (sequence, head), four warps of 16 rows.  K / V tiles of 64 tokens stream
+// One CTA = 128 query rows of one (sequence, head), four warps of 32 rows (64 and 16 for head size 256).  K / V tiles of 64 tokens stream
 // through a double-buffered shared-memory ring (cp.async, 16 bytes per thread, XOR-swizzled so that ldmatrix is
 // conflict-free); S = Q K^T and O += P V run on warp-level m16n8k16 MMAs with P taken straight from the S
 // accumulators.  Later query tiles do more work (causal), so tiles are issued longest first.
 // This is a dense contraction, bounded by the tensor pipe, unlike the rest of the library.
 #include "pa_common.cuh"
 #include "pa_launch.h"
+#include "pa_prefill.h"
+
+#include <cstdlib>
 
 namespace pa {
 namespace {
 
-constexpr int PF_BM = 64;   // query rows per CTA
+// PF_MT = 16-row MMA tiles per warp (template parameter): every K / V fragment read from shared memory feeds
+// PF_MT MMAs, so two tiles halve the shared-memory traffic per flop; head size 256 keeps one (accumulator registers).
 constexpr int PF_BN = 64;   // kv tokens per tile
 constexpr int PF_THREADS = 128;
-
-struct PrefillParams {
-  void* out;
-  const void* q;
-  const void* k;
-  const void* v;
-  const uint32_t* cu_seqlens;   // [num_seqs + 1]
-  const float* alibi_slopes;    // may be null
-  int64_t q_stride, k_stride, v_stride, o_stride;   // token strides, elements
-  int num_heads, num_kv_heads, max_seqlen;
-  float scale, softcap;
-};
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;   // zero-fill when the row lies outside the sequence
@@ -54,9 +46,10 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return static_cast<uint32_t>(r * (HEAD * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <typename T, int HEAD>
+template <typename T, int HEAD, int PF_MT>
 __global__ void __launch_bounds__(PF_THREADS)
 prefill_attention_kernel(const PrefillParams p) {
+  constexpr int PF_BM = 64 * PF_MT;   // query rows per CTA (four warps)
   constexpr int CH = HEAD / 8;        // 16-byte chunks per row
   constexpr int KS = HEAD / 16;       // k-steps of S = Q K^T
   constexpr int NT_S = PF_BN / 8;     // n-tiles of S
@@ -84,15 +77,15 @@ prefill_attention_kernel(const PrefillParams p) {
   const T* vg = reinterpret_cast<const T*>(p.v) + static_cast<int64_t>(tok_lo) * p.v_stride + kvh * HEAD;
 
   // ---- loads: 64 rows x CH chunks, 128 threads
-  auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int row0, int rows_valid) {
-#pragma unroll
-    for (int i = threadIdx.x; i < PF_BN * CH; i += PF_THREADS) {
+  auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int row0, int rows_valid, int rows = PF_BN) {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < rows * CH; i += PF_THREADS) {
       const int r = i / CH, c = i % CH;
       cp_async16(dst + swz<HEAD>(r, c), src + static_cast<int64_t>(row0 + r) * stride + c * 8, r < rows_valid);
     }
   };
-  load_tile(sQ, qg, p.q_stride, 0, len - q0);
-  const int n_kv_tiles = qt + 1;                   // causal: kv tiles 0..qt
+  load_tile(sQ, qg, p.q_stride, 0, len - q0, PF_BM);
+  const int n_kv_tiles = min((q0 + PF_BM + PF_BN - 1) / PF_BN, (len + PF_BN - 1) / PF_BN);   // causal: keys up to the last query row
   load_tile(sK, kg, p.k_stride, 0, len);
   load_tile(sV, vg, p.v_stride, 0, len);
   cp_async_commit();
@@ -100,11 +93,15 @@ prefill_attention_kernel(const PrefillParams p) {
   const float slope = p.alibi_slopes ? p.alibi_slopes[head] : 0.f;
   const bool capped = p.softcap != 1.0f;
   const float scale_log2 = p.scale * LOG2E;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[NT_O][4];
+  float m[PF_MT][2], l[PF_MT][2];
+  float o[PF_MT][NT_O][4];
 #pragma unroll
-  for (int n = 0; n < NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  uint32_t qa[KS][4];
+  for (int t = 0; t < PF_MT; ++t) {
+    m[t][0] = m[t][1] = -INFINITY;
+    l[t][0] = l[t][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n) o[t][n][0] = o[t][n][1] = o[t][n][2] = o[t][n][3] = 0.f;
+  }
 
   for (int j = 0; j < n_kv_tiles; ++j) {
     const int buf = j & 1;
@@ -117,114 +114,135 @@ prefill_attention_kernel(const PrefillParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (j == 0) {                                  // this warp's 16 query rows as A fragments, kept in registers
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
-        ldmatrix_x4(sQ + swz<HEAD>(r, c), qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
-      }
-    }
     const uint32_t kt = sK + buf * TILE_BYTES, vt = sV + buf * TILE_BYTES;
+    if (j * PF_BN <= q0 + warp * (16 * PF_MT) + 16 * PF_MT - 1) {   // else: every key of the tile lies after this warp's rows
 
-    // ---- S = Q K^T (16 x 64 per warp)
-    float s[NT_S][4];
+    // ---- S = Q K^T (PF_MT x 16 rows x 64 keys per warp); Q fragments are re-read from shared memory per k-step
+    float s[PF_MT][NT_S][4];
 #pragma unroll
-    for (int n = 0; n < NT_S; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int t = 0; t < PF_MT; ++t)
+#pragma unroll
+      for (int n = 0; n < NT_S; ++n) s[t][n][0] = s[t][n][1] = s[t][n][2] = s[t][n][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
+      uint32_t qa[PF_MT][4];
+#pragma unroll
+      for (int t = 0; t < PF_MT; ++t) {
+        const int r = (warp * PF_MT + t) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = ks * 2 + (lane >> 4);
+        ldmatrix_x4(sQ + swz<HEAD>(r, c), qa[t][0], qa[t][1], qa[t][2], qa[t][3]);
+      }
 #pragma unroll
       for (int n = 0; n < NT_S; n += 2) {
         const int r = n * 8 + (lane & 7) + (lane >> 4) * 8, c = ks * 2 + ((lane >> 3) & 1);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(kt + swz<HEAD>(r, c), b0, b1, b2, b3);
-        mma16816<T>(s[n], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-        mma16816<T>(s[n + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+#pragma unroll
+        for (int t = 0; t < PF_MT; ++t) {
+          mma16816<T>(s[t][n], qa[t][0], qa[t][1], qa[t][2], qa[t][3], b0, b1);
+          mma16816<T>(s[t][n + 1], qa[t][0], qa[t][1], qa[t][2], qa[t][3], b2, b3);
+        }
       }
     }
 
-    // ---- logits (log2 domain), causal / length mask, online softmax for rows gi and gi + 8
-    const int row0 = q0 + warp * 16 + gi;          // query position within the sequence
-    const bool diag = (j == n_kv_tiles - 1);
+    // ---- logits (log2 domain), causal / length mask, online softmax for rows gi and gi + 8 of every tile
+    const bool need_mask = (j + 1) * PF_BN > q0 + 1 || (j + 1) * PF_BN > len;   // tile touches the diagonal or the end
 #pragma unroll
-    for (int n = 0; n < NT_S; ++n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = j * PF_BN + n * 8 + 2 * qi + (e & 1);   // key position
-        const int row = row0 + (e >> 1) * 8;
-        float x = s[n][e];
-        if (capped) x = tanh_approx(x * p.scale / p.softcap) * p.softcap * LOG2E;
-        else x *= scale_log2;
-        if (slope != 0.f) x += slope * LOG2E * static_cast<float>(col - row);
-        if (col >= len || (diag && col > row)) x = -INFINITY;
-        s[n][e] = x;
-      }
-    }
-    float corr[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float mx = -INFINITY;
-#pragma unroll
-      for (int n = 0; n < NT_S; ++n) mx = fmaxf(mx, fmaxf(s[n][2 * h], s[n][2 * h + 1]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float mn = fmaxf(m[h], mx);
-      const float base = mn == -INFINITY ? 0.f : mn;   // a row past the sequence end sees no key at all
-      corr[h] = exp2_approx(m[h] - base);
-      float sum = 0.f;
+    for (int t = 0; t < PF_MT; ++t) {
+      const int row0 = q0 + (warp * PF_MT + t) * 16 + gi;          // query position within the sequence
 #pragma unroll
       for (int n = 0; n < NT_S; ++n) {
-        s[n][2 * h] = exp2_approx(s[n][2 * h] - base);
-        s[n][2 * h + 1] = exp2_approx(s[n][2 * h + 1] - base);
-        sum += s[n][2 * h] + s[n][2 * h + 1];
-      }
-      l[h] = l[h] * corr[h] + sum;
-      m[h] = mn;
-    }
 #pragma unroll
-    for (int n = 0; n < NT_O; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        for (int e = 0; e < 4; ++e) {
+          const int col = j * PF_BN + n * 8 + 2 * qi + (e & 1);   // key position
+          const int row = row0 + (e >> 1) * 8;
+          float x = s[t][n][e];
+          if (capped) x = tanh_approx(x * p.scale / p.softcap) * p.softcap * LOG2E;
+          else x *= scale_log2;
+          if (slope != 0.f) x += slope * LOG2E * static_cast<float>(col - row);
+          if (need_mask && (col >= len || col > row)) x = -INFINITY;
+          s[t][n][e] = x;
+        }
+      }
+      float corr[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < NT_S; ++n) mx = fmaxf(mx, fmaxf(s[t][n][2 * h], s[t][n][2 * h + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float mn = fmaxf(m[t][h], mx);
+        const float base = mn == -INFINITY ? 0.f : mn;   // a row whose keys are all masked so far
+        corr[h] = exp2_approx(m[t][h] - base);
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT_S; ++n) {
+          s[t][n][2 * h] = exp2_approx(s[t][n][2 * h] - base);
+          s[t][n][2 * h + 1] = exp2_approx(s[t][n][2 * h + 1] - base);
+          sum += s[t][n][2 * h] + s[t][n][2 * h + 1];
+        }
+        l[t][h] = l[t][h] * corr[h] + sum;
+        m[t][h] = mn;
+      }
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        o[t][n][0] *= corr[0]; o[t][n][1] *= corr[0]; o[t][n][2] *= corr[1]; o[t][n][3] *= corr[1];
+      }
     }
 
     // ---- O += P V
 #pragma unroll
     for (int kk = 0; kk < PF_BN / 16; ++kk) {
-      const uint32_t a0 = pack2<T>(s[2 * kk][0], s[2 * kk][1]), a1 = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
-      const uint32_t a2 = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      uint32_t pa[PF_MT][4];
+#pragma unroll
+      for (int t = 0; t < PF_MT; ++t) {
+        pa[t][0] = pack2<T>(s[t][2 * kk][0], s[t][2 * kk][1]);
+        pa[t][1] = pack2<T>(s[t][2 * kk][2], s[t][2 * kk][3]);
+        pa[t][2] = pack2<T>(s[t][2 * kk + 1][0], s[t][2 * kk + 1][1]);
+        pa[t][3] = pack2<T>(s[t][2 * kk + 1][2], s[t][2 * kk + 1][3]);
+      }
 #pragma unroll
       for (int n = 0; n < NT_O; n += 2) {
         const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = n + (lane >> 4);
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4_trans(vt + swz<HEAD>(r, c), b0, b1, b2, b3);
-        mma16816<T>(o[n], a0, a1, a2, a3, b0, b1);
-        mma16816<T>(o[n + 1], a0, a1, a2, a3, b2, b3);
+#pragma unroll
+        for (int t = 0; t < PF_MT; ++t) {
+          mma16816<T>(o[t][n], pa[t][0], pa[t][1], pa[t][2], pa[t][3], b0, b1);
+          mma16816<T>(o[t][n + 1], pa[t][0], pa[t][1], pa[t][2], pa[t][3], b2, b3);
+        }
       }
+    }
     }
     __syncthreads();   // the buffer just read is the target of the next iteration's prefetch
   }
 
   // ---- normalise and store
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-  }
   T* og = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + q0) * p.o_stride + head * HEAD;
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + gi + h * 8;
-    if (q0 + r < len) {
-      const float inv = 1.0f / l[h];
+  for (int t = 0; t < PF_MT; ++t) {
 #pragma unroll
-      for (int n = 0; n < NT_O; ++n)
-        *reinterpret_cast<uint32_t*>(og + static_cast<int64_t>(r) * p.o_stride + n * 8 + 2 * qi) =
-            pack2<T>(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    for (int h = 0; h < 2; ++h) {
+      float lt = l[t][h];
+      lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+      lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+      const int r = (warp * PF_MT + t) * 16 + gi + h * 8;
+      if (q0 + r < len) {
+        const float inv = 1.0f / lt;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+          *reinterpret_cast<uint32_t*>(og + static_cast<int64_t>(r) * p.o_stride + n * 8 + 2 * qi) =
+              pack2<T>(o[t][n][2 * h] * inv, o[t][n][2 * h + 1] * inv);
+      }
     }
   }
 }
 
 template <typename T, int HEAD>
 int launch_prefill(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
-  auto kernel = prefill_attention_kernel<T, HEAD>;
+  constexpr int PF_MT = HEAD <= 128 ? 2 : 1;
+  constexpr int PF_BM = 64 * PF_MT;
+  auto kernel = prefill_attention_kernel<T, HEAD, PF_MT>;
   constexpr int smem = (PF_BM + 4 * PF_BN) * HEAD * 2;
   static bool configured[64] = {};
   int dev = 0;
@@ -273,8 +291,18 @@ extern "C" int paged_prefill_attention(void* out, const void* query, const void*
   p.max_seqlen = max_seqlen;
   p.scale = scale;
   p.softcap = softcapping;
+  p.status = device_status_word();
+  if (!p.status) return fail(PA_ERR_CUDA, "could not set up the device status word");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // Head sizes 64 and 128 run on tcgen05 / tensor memory; PA_PREFILL_WARP_MMA=1 selects the warp-level MMA
+  // kernel for them too (comparison runs), as head size 256 always does.
+  const char* env = std::getenv("PA_PREFILL_WARP_MMA");   // read per call: a test switches it between calls
+  const bool warp_mma_only = env && env[0] == '1';
   int rc = PA_ERR_UNSUPPORTED;
+  if (!warp_mma_only && (head_size == 64 || head_size == 128)) {
+    rc = launch_prefill_umma(p, num_seqs, head_size, dtype, s);
+    return rc == PA_OK ? rc : fail(rc, "prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
   if (dtype == DT_BF16) {
     if (head_size == 64) rc = launch_prefill<__nv_bfloat16, 64>(p, num_seqs, s);
     else if (head_size == 128) rc = launch_prefill<__nv_bfloat16, 128>(p, num_seqs, s);

@@ -1,0 +1,25 @@
+// Argument bundle and launcher prototypes of the prefill (prompt) attention kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pa {
+
+struct PrefillParams {
+  void* out;
+  const void* q;
+  const void* k;
+  const void* v;
+  const uint32_t* cu_seqlens;   // [num_seqs + 1]
+  const float* alibi_slopes;    // may be null
+  unsigned* status;             // device status word (bounded waits report here)
+  int64_t q_stride, k_stride, v_stride, o_stride;   // token strides, elements
+  int num_heads, num_kv_heads, max_seqlen;
+  float scale, softcap;
+};
+
+// tcgen05 / TMEM kernel (head sizes 64 and 128).  Returns PA_ERR_UNSUPPORTED for other head sizes.
+int launch_prefill_umma(const PrefillParams& p, int num_seqs, int head_size, uint32_t dtype, cudaStream_t stream);
+
+}  // namespace pa

@@ -1,0 +1,406 @@
+// Causal self-attention over packed variable-length prompts on the fifth-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory).  Same function as prefill_attention_kernel in
+// pa_prefill.cu (which restates src/lib.rs:87-213 of the reference); this is the kernel that runs for
+// head sizes 64 and 128.
+//
+// One CTA = 128 query rows of one (sequence, head); thread t owns row t, which is lane t of tensor memory.
+// Per 64-key tile:
+//   S = Q K^T      tcgen05.mma, A = Q and B = K from shared memory (K-major, 128-byte swizzle), D = 64 columns
+//   softmax        each thread reads its whole row of S with tcgen05.ld: no shuffles; P (16-bit) goes back to
+//                  tensor memory with tcgen05.st
+//   O += P V       tcgen05.mma, A = P from tensor memory, B = V from shared memory (MN-major), D = HEAD columns
+// O stays in tensor memory for the whole CTA.  It is rescaled only when a row maximum grows by more than
+// 2^8 over the reference value the exponentials use (the exact result does not depend on that reference),
+// which after the first tiles is rare.  One thread issues the MMAs; S of tile j + 1 is issued directly
+// behind P V of tile j, and tcgen05.commit on an mbarrier tells the CTA when S is there.  MMAs complete in
+// issue order, so that arrival also says P V of the tile before is done: its V buffer and O are free.
+// Two CTAs fit on an SM (256 tensor-memory columns and ~97 KB of shared memory each); while one does its
+// softmax the other one's MMAs run.  K / V tiles arrive by cp.async into a two-deep ring, written with
+// the 128-byte swizzle the MMA descriptors name.
+//
+// Every wait is bounded (pa_common.cuh); a CTA that gives up records it in the device status word, frees
+// its tensor memory and returns.
+#include "pa_common.cuh"
+#include "pa_launch.h"
+#include "pa_prefill.h"
+
+#include <type_traits>
+
+namespace pa {
+namespace {
+
+constexpr int UM_BM = 128;   // query rows per CTA = tensor-memory lanes
+constexpr int UM_BN = 64;    // keys per tile
+constexpr int UM_THREADS = 128;
+constexpr float UM_RESCALE_GAP = 8.0f;   // log2 units a row maximum may exceed its reference before O is rescaled
+
+// ---------------------------------------------------------------- PTX wrappers (tcgen05)
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // zero-fill when the row lies outside the sequence
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Orders this thread's generic-proxy writes to shared memory before later async-proxy reads (the MMA).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 consecutive columns of this thread's lane.  The wait names the registers as read-write operands so that
+// no use of them can be scheduled before it.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                 "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (64 bits): start address >> 4 in bits [0,14), leading byte offset >> 4 in
+// [16,30), stride byte offset >> 4 in [32,46), descriptor version 1 in [46,48), layout 2 = 128-byte swizzle in [61,64).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor of kind::f16: D format f32 (bits [4,6) = 1), A / B format in [7,10) / [10,13)
+// (0 = f16, 1 = bf16), B MN-major flag in bit 16, N / 8 in [17,23), M / 16 in [24,29).
+template <typename T>
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
+  const uint32_t fmt = sizeof(T) == 2 && !std::is_same<T, __half>::value ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// Byte offset of element (r, 8 * c) in a tile of `rows` rows stored as HEAD / 64 column blocks of [rows][128 bytes],
+// 16-byte chunks XOR-swizzled with the row (the 128-byte swizzle pattern; blocks are 1024-byte aligned).
+__device__ __forceinline__ uint32_t tile_off(int rows, int r, int c) {
+  return static_cast<uint32_t>((c >> 3) * (rows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+template <typename T, int HEAD>
+__global__ void __launch_bounds__(UM_THREADS)
+prefill_umma_kernel(const PrefillParams p) {
+  constexpr int CH = HEAD / 8;                 // 16-byte chunks per row
+  constexpr int Q_BYTES = UM_BM * HEAD * 2;
+  constexpr int KV_BYTES = UM_BN * HEAD * 2;
+  constexpr uint32_t TM_COLS = 256;            // power of two >= HEAD + 64 + 32; two CTAs share the SM's 512
+  constexpr uint32_t COL_O = 0, COL_S = HEAD, COL_P = HEAD + UM_BN;
+  constexpr uint32_t IDESC_S = instr_desc<T>(UM_BM, UM_BN, false);
+  constexpr uint32_t IDESC_O = instr_desc<T>(UM_BM, HEAD, true);
+  static_assert(HEAD == 64 || HEAD == 128, "tensor-memory budget and descriptors are laid out for these head sizes");
+
+  const int seq = blockIdx.y, head = blockIdx.z;
+  const int tok_lo = static_cast<int>(p.cu_seqlens[seq]), tok_hi = static_cast<int>(p.cu_seqlens[seq + 1]);
+  const int len = tok_hi - tok_lo;
+  const int ntiles = (len + UM_BM - 1) / UM_BM;
+  const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // heaviest (last) tiles first
+  if (qt >= ntiles) return;                     // before any tensor memory is taken
+  const int kvh = head / (p.num_heads / p.num_kv_heads);
+  const int q0 = qt * UM_BM;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_kv = min((q0 + UM_BM + UM_BN - 1) / UM_BN, (len + UM_BN - 1) / UM_BN);   // causal: keys up to the last row
+
+  extern __shared__ unsigned char um_smem_raw[];
+  const uint32_t smem0 = (smem_addr(um_smem_raw) + 1023u) & ~1023u;   // swizzle atoms are 1024-byte aligned
+  const uint32_t sQ = smem0;
+  const uint32_t sK = sQ + Q_BYTES;            // 2 tiles
+  const uint32_t sV = sK + 2 * KV_BYTES;       // 2 tiles
+  const uint32_t bar_s = sV + 2 * KV_BYTES;    // S of a tile is in tensor memory (and every MMA before it is done)
+  const uint32_t bar_o = bar_s + 8;            // the last P V is done
+  const uint32_t tm_slot = bar_o + 8;
+  unsigned char* um_smem = um_smem_raw + (smem0 - smem_addr(um_smem_raw));
+
+  const T* qg = reinterpret_cast<const T*>(p.q) + static_cast<int64_t>(tok_lo + q0) * p.q_stride + head * HEAD;
+  const T* kg = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(tok_lo) * p.k_stride + kvh * HEAD;
+  const T* vg = reinterpret_cast<const T*>(p.v) + static_cast<int64_t>(tok_lo) * p.v_stride + kvh * HEAD;
+
+  auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int rows, int row0, int rows_valid) {
+#pragma unroll 4
+    for (int i = tid; i < rows * CH; i += UM_THREADS) {
+      const int r = i / CH, c = i % CH;
+      cp_async16(dst + tile_off(rows, r, c), src + static_cast<int64_t>(row0 + r) * stride + c * 8, r < rows_valid);
+    }
+  };
+  auto load_k = [&](int j) { load_tile(sK + (j & 1) * KV_BYTES, kg, p.k_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
+  auto load_v = [&](int j) { load_tile(sV + (j & 1) * KV_BYTES, vg, p.v_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
+
+  // ---- prologue: group 0 = {Q, K0}, group 1 = {K1, V0}
+  load_tile(sQ, qg, p.q_stride, UM_BM, 0, len - q0);
+  load_k(0);
+  cp_async_commit();
+  if (n_kv > 1) load_k(1);
+  load_v(0);
+  cp_async_commit();
+
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(tm_slot, TM_COLS);
+    tmem_relinquish();
+  }
+  cp_async_wait<1>();
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm_base = *reinterpret_cast<volatile uint32_t*>(um_smem + (tm_slot - smem0));
+  const uint32_t tm_lane = tm_base + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's 32 lanes
+
+  // S_j = Q K_j^T: HEAD / 16 MMAs of K = 16 (32 bytes along the swizzled rows; 64-element blocks 16 / 8 KB apart).
+  auto issue_s = [&](int j) {
+    const uint32_t kb = sK + (j & 1) * KV_BYTES;
+#pragma unroll
+    for (int ks = 0; ks < HEAD / 16; ++ks) {
+      const uint64_t a = smem_desc(sQ + (ks >> 2) * (UM_BM * 128) + (ks & 3) * 32, 16, 1024);
+      const uint64_t b = smem_desc(kb + (ks >> 2) * (UM_BN * 128) + (ks & 3) * 32, 16, 1024);
+      umma_ss(tm_base + COL_S, a, b, IDESC_S, ks > 0);
+    }
+    tc_commit(bar_s);
+  };
+  // O (+)= P_j V_j: 4 MMAs of K = 16 keys (two 8-key groups = 2048 bytes); V is MN-major: 64-element blocks
+  // UM_BN * 128 bytes apart (leading offset), 8-key groups 1024 bytes apart (stride offset).
+  auto issue_o = [&](int j, bool last) {
+    const uint32_t vb = sV + (j & 1) * KV_BYTES;
+#pragma unroll
+    for (int kk = 0; kk < UM_BN / 16; ++kk) {
+      const uint64_t b = smem_desc(vb + kk * 2048, UM_BN * 128, 1024);
+      umma_ts(tm_base + COL_O, tm_base + COL_P + kk * 8, b, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+    }
+    if (last) tc_commit(bar_o);
+  };
+
+  if (tid == 0) issue_s(0);
+  __syncwarp();
+
+  const float slope = p.alibi_slopes ? p.alibi_slopes[head] * LOG2E : 0.f;
+  const bool capped = p.softcap != 1.0f;
+  const float scale_log2 = p.scale * LOG2E;
+  const int row = q0 + tid;                    // this thread's query position within the sequence
+  float m_ref = 0.f, l = 0.f;
+  bool ok = true;
+
+  for (int j = 0; j < n_kv; ++j) {
+    ok = mbar_wait(bar_s, j & 1, p.status) && ok;
+    tc_fence_after();
+    // S_j is complete and so is every MMA before it: K buffer j & 1 and V buffer (j + 1) & 1 are free.
+    if (j + 2 < n_kv) load_k(j + 2);
+    if (j + 1 < n_kv) load_v(j + 1);
+    cp_async_commit();
+
+    float s[UM_BN];
+    {
+      uint32_t lo[32], hi[32];
+      tmem_ld32(tm_lane + COL_S, lo);
+      tmem_ld32(tm_lane + COL_S + 32, hi);
+      tmem_ld_wait(lo);
+      tmem_ld_wait(hi);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        s[i] = __uint_as_float(lo[i]);
+        s[32 + i] = __uint_as_float(hi[i]);
+      }
+    }
+    const int col0 = j * UM_BN;
+    const bool plain = !capped && slope == 0.f && scale_log2 > 0.f && col0 + UM_BN <= q0 + 1 && col0 + UM_BN <= len;
+    float mx = -INFINITY;
+    if (plain) {                               // no mask, no bias: scale folded into the exponent's FMA
+#pragma unroll
+      for (int i = 0; i < UM_BN; ++i) mx = fmaxf(mx, s[i]);
+      mx *= scale_log2;
+    } else {
+#pragma unroll
+      for (int i = 0; i < UM_BN; ++i) {
+        const int col = col0 + i;
+        float x = s[i];
+        if (capped) x = tanh_approx(x * p.scale / p.softcap) * p.softcap * LOG2E;
+        else x *= scale_log2;
+        x += slope * static_cast<float>(col - row);
+        if (col >= len || col > row) x = -INFINITY;
+        s[i] = x;
+        mx = fmaxf(mx, x);
+      }
+    }
+    // Reference value of the exponentials.  Tile 0 always holds key 0, which no row masks, so mx is finite there.
+    float corr = 1.f;
+    bool grow = false;
+    if (j == 0) {
+      m_ref = mx;
+    } else if (mx > m_ref + UM_RESCALE_GAP) {
+      corr = exp2_approx(m_ref - mx);
+      m_ref = mx;
+      grow = true;
+    }
+    uint32_t pk[32];
+    float sum = 0.f;
+    if (plain) {
+#pragma unroll
+      for (int i = 0; i < UM_BN; i += 2) {
+        const float a = exp2_approx(fmaf(s[i], scale_log2, -m_ref)), b = exp2_approx(fmaf(s[i + 1], scale_log2, -m_ref));
+        sum += a + b;
+        pk[i >> 1] = pack2<T>(a, b);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < UM_BN; i += 2) {
+        const float a = exp2_approx(s[i] - m_ref), b = exp2_approx(s[i + 1] - m_ref);
+        sum += a + b;
+        pk[i >> 1] = pack2<T>(a, b);
+      }
+    }
+    l = l * corr + sum;
+    if (__any_sync(0xffffffffu, grow)) {       // warp-uniform: tcgen05.ld / st are warp-wide
+#pragma unroll
+      for (int c = 0; c < HEAD; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tm_lane + COL_O + c, o);
+        tmem_ld_wait(o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+        tmem_st32(tm_lane + COL_O + c, o);
+      }
+    }
+    tmem_st32(tm_lane + COL_P, pk);
+    tmem_st_wait();
+    cp_async_wait<1>();                        // V_j and K_{j+1} have landed (this thread's part)
+    fence_proxy_async();
+    tc_fence_before();
+    if (!__syncthreads_and(ok)) { ok = false; break; }
+    if (tid == 0) {
+      tc_fence_after();
+      issue_o(j, j + 1 == n_kv);
+      if (j + 1 < n_kv) issue_s(j + 1);
+    }
+    __syncwarp();
+  }
+
+  if (ok) ok = mbar_wait(bar_o, 0, p.status);
+  ok = __syncthreads_and(ok);                  // uniform from here on: the tensor-memory loads below are warp-wide
+  tc_fence_after();
+  if (ok) {
+    // ---- normalise and store this thread's row (rows past the end of the sequence only take part in the loads)
+    const float inv = 1.0f / l;
+    T* og = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + row) * p.o_stride + head * HEAD;
+    const bool wide = reinterpret_cast<uintptr_t>(og) % 16 == 0;
+#pragma unroll
+    for (int c = 0; c < HEAD; c += 32) {
+      uint32_t o[32];
+      tmem_ld32(tm_lane + COL_O + c, o);
+      tmem_ld_wait(o);
+      if (row < len) {
+        if (wide) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = pack2<T>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = pack2<T>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = pack2<T>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(og + c + i) = w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            *reinterpret_cast<uint32_t*>(og + c + i) = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+        }
+      }
+      __syncwarp();
+    }
+  }
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tm_base, TM_COLS);
+}
+
+template <typename T, int HEAD>
+int launch_umma(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
+  auto kernel = prefill_umma_kernel<T, HEAD>;
+  constexpr int smem = UM_BM * HEAD * 2 + 4 * UM_BN * HEAD * 2 + 32 + 1024;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return PA_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return PA_ERR_CUDA;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid((p.max_seqlen + UM_BM - 1) / UM_BM, num_seqs, p.num_heads);
+  kernel<<<grid, UM_THREADS, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+}  // namespace
+
+int launch_prefill_umma(const PrefillParams& p, int num_seqs, int head_size, uint32_t dtype, cudaStream_t stream) {
+  if (dtype == DT_BF16) {
+    if (head_size == 64) return launch_umma<__nv_bfloat16, 64>(p, num_seqs, stream);
+    if (head_size == 128) return launch_umma<__nv_bfloat16, 128>(p, num_seqs, stream);
+  } else if (dtype == DT_F16) {
+    if (head_size == 64) return launch_umma<__half, 64>(p, num_seqs, stream);
+    if (head_size == 128) return launch_umma<__half, 128>(p, num_seqs, stream);
+  }
+  return PA_ERR_UNSUPPORTED;
+}
+
+}  // namespace pa

@@ -10,7 +10,18 @@ from tests.helpers import DT, from_torch_f32, to_torch, tolerances
 pytestmark = pytest.mark.gpu
 
 
-def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0):
+@pytest.fixture(params=["tcgen05", "warp_mma"])
+def kernel(request, monkeypatch):
+    """Head sizes 64 and 128 run on the tcgen05 kernel; PA_PREFILL_WARP_MMA=1 sends them to the warp-level MMA
+    kernel, which head size 256 always uses.  The library reads the variable per call."""
+    if request.param == "warp_mma":
+        monkeypatch.setenv("PA_PREFILL_WARP_MMA", "1")
+    else:
+        monkeypatch.delenv("PA_PREFILL_WARP_MMA", raising=False)
+    return request.param
+
+
+def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0, key_growth=0.0):
     import torch
     import attention_rs_b200 as pa
     dev = torch.device("cuda:0")
@@ -19,7 +30,10 @@ def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0)
     nt = int(sum(lens))
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
     q = O.to_storage(rng.standard_normal((nt, nh + fused_pad, hs), dtype=np.float32), dt)
-    k = O.to_storage(rng.standard_normal((nt, nkv + fused_pad, hs), dtype=np.float32), dt)
+    kf = rng.standard_normal((nt, nkv + fused_pad, hs), dtype=np.float32)
+    if key_growth:   # logits that keep growing along the prompt: the running maximum moves by many powers of two
+        kf *= (1.0 + key_growth * np.arange(nt, dtype=np.float32))[:, None, None]
+    k = O.to_storage(kf, dt)
     v = O.to_storage(rng.standard_normal((nt, nkv + fused_pad, hs), dtype=np.float32), dt)
     slopes = np.array([2.0 ** (-8.0 * (i + 1) / nh) for i in range(nh)], dtype=np.float32) if alibi else None
     scale = 1.0 / math.sqrt(hs)
@@ -29,6 +43,7 @@ def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0)
                                None if slopes is None else torch.from_numpy(slopes).to(dev))
     torch.cuda.synchronize()
     got = from_torch_f32(got)
+    assert pa.ops.device_status() == 0
     assert not np.isnan(got).any()
     mx, mean = tolerances(dtype)
     err = np.abs(got - want)
@@ -37,17 +52,20 @@ def run(lens, nh, nkv, hs, dtype, softcap=1.0, alibi=False, seed=0, fused_pad=0)
 
 @pytest.mark.parametrize("dtype", ["bf16", "f16"])
 @pytest.mark.parametrize("hs", [64, 128, 256])
-def test_prefill_lengths_around_tile_edges(dtype, hs):
+def test_prefill_lengths_around_tile_edges(dtype, hs, kernel):
     run([1, 63, 64, 65, 127, 129, 200], 4, 2, hs, dtype, seed=hs)
 
 
-def test_prefill_variants():
+def test_prefill_variants(kernel):
     run([300, 5], 8, 8, 128, "bf16", seed=1)                       # MHA
     run([90, 260], 8, 1, 128, "f16", seed=2)                        # MQA
     run([150, 77], 4, 2, 128, "bf16", softcap=30.0, seed=3)
     run([150, 77], 4, 2, 64, "f16", alibi=True, seed=4)
     run([150, 77], 4, 2, 128, "bf16", seed=5, fused_pad=3)          # rows sliced out of wider tensors
     run([700], 2, 1, 128, "bf16", seed=6)                           # many kv tiles
+    run([512, 130], 2, 1, 128, "bf16", seed=7, key_growth=1 / 32)   # accumulator rescaled again and again
+    run([700], 2, 2, 64, "f16", seed=8, key_growth=1 / 64)
+    run([1, 1, 2, 0, 3], 2, 1, 128, "bf16", seed=9)                 # tiny and empty prompts
 
 
 def test_prefill_rejects_unsupported():
