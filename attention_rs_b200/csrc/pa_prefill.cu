@@ -17,6 +17,7 @@
 #include "pa_prefill.h"
 
 #include <cstdlib>
+#include <cstring>
 
 namespace pa {
 namespace {
@@ -260,14 +261,14 @@ int launch_prefill(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
 }  // namespace pa
 
 extern "C" int paged_prefill_attention(void* out, const void* query, const void* key, const void* value,
-                                       const uint32_t* cu_seqlens, int32_t num_seqs, int32_t max_seqlen,
+                                       const uint32_t* cu_seqlens, int32_t num_seqs, int32_t total_tokens, int32_t max_seqlen,
                                        int32_t num_heads, int32_t num_kv_heads, int32_t head_size, int32_t q_stride,
                                        int32_t k_stride, int32_t v_stride, int32_t out_stride, float scale,
                                        float softcapping, const float* alibi_slopes, uint32_t dtype, int64_t stream) {
   using namespace pa;
-  if (num_seqs == 0 || max_seqlen == 0) return PA_OK;
+  if (num_seqs == 0 || max_seqlen == 0 || total_tokens == 0) return PA_OK;
   if (!out || !query || !key || !value || !cu_seqlens) return fail(PA_ERR_INVALID_ARGUMENT, "null pointer passed to paged_prefill_attention");
-  if (num_seqs < 0 || num_seqs > 65535 || max_seqlen < 0 || num_heads <= 0 || num_heads > 65535 || num_kv_heads <= 0 ||
+  if (num_seqs < 0 || num_seqs > 65535 || max_seqlen < 0 || total_tokens < 0 || num_heads <= 0 || num_heads > 65535 || num_kv_heads <= 0 ||
       num_heads % num_kv_heads != 0)
     return fail(PA_ERR_INVALID_ARGUMENT, "bad sizes passed to paged_prefill_attention");
   if (dtype != DT_F16 && dtype != DT_BF16) return fail(PA_ERR_UNSUPPORTED, "prefill attention takes f16 or bf16 tensors");
@@ -294,13 +295,17 @@ extern "C" int paged_prefill_attention(void* out, const void* query, const void*
   p.status = device_status_word();
   if (!p.status) return fail(PA_ERR_CUDA, "could not set up the device status word");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // Head sizes 64 and 128 run on tcgen05 / tensor memory; PA_PREFILL_WARP_MMA=1 selects the warp-level MMA
-  // kernel for them too (comparison runs), as head size 256 always does.
-  const char* env = std::getenv("PA_PREFILL_WARP_MMA");   // read per call: a test switches it between calls
-  const bool warp_mma_only = env && env[0] == '1';
+  // Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel.  PA_PREFILL_KERNEL selects another one for
+  // them (comparison runs; read per call so that a test can switch between calls): "tcgen05_simple" or "warp_mma",
+  // the kernel head size 256 always uses.
+  const char* env = std::getenv("PA_PREFILL_KERNEL");
+  const bool want_warp_mma = env && std::strcmp(env, "warp_mma") == 0;
+  const bool want_simple = env && std::strcmp(env, "tcgen05_simple") == 0;
   int rc = PA_ERR_UNSUPPORTED;
-  if (!warp_mma_only && (head_size == 64 || head_size == 128)) {
-    rc = launch_prefill_umma(p, num_seqs, head_size, dtype, s);
+  if (!want_warp_mma && (head_size == 64 || head_size == 128)) {
+    rc = want_simple ? launch_prefill_umma(p, num_seqs, head_size, dtype, s)
+                     : launch_prefill_ws(p, num_seqs, total_tokens, head_size, dtype, s);
+    if (rc == PA_ERR_UNSUPPORTED) return fail(rc, "prefill attention could not describe q / k / v to the TMA unit");
     return rc == PA_OK ? rc : fail(rc, "prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
   }
   if (dtype == DT_BF16) {

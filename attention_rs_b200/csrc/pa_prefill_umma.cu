@@ -135,6 +135,13 @@ __device__ __forceinline__ uint32_t tile_off(int rows, int r, int c) {
   return static_cast<uint32_t>((c >> 3) * (rows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+#ifdef PA_DEBUG_PF_TIMING
+__device__ long long g_pf_timing[64 * 8];
+#define PF_STAMP(k) do { if (dbg && j < 64) g_pf_timing[j * 8 + (k)] = clock64(); } while (0)
+#else
+#define PF_STAMP(k) do { } while (0)
+#endif
+
 template <typename T, int HEAD>
 __global__ void __launch_bounds__(UM_THREADS)
 prefill_umma_kernel(const PrefillParams p) {
@@ -172,12 +179,16 @@ prefill_umma_kernel(const PrefillParams p) {
   const T* kg = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(tok_lo) * p.k_stride + kvh * HEAD;
   const T* vg = reinterpret_cast<const T*>(p.v) + static_cast<int64_t>(tok_lo) * p.v_stride + kvh * HEAD;
 
+  // Thread t copies chunk column t % CH of rows t / CH + k * (128 / CH): the column, and with it the swizzle term
+  // (rows advance by a multiple of 8), are fixed per thread, so one shared and one global offset serve every copy.
+  constexpr int RSTEP = UM_THREADS / CH;
+  const int lr = tid / CH, lc = tid % CH;
   auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int rows, int row0, int rows_valid) {
-#pragma unroll 4
-    for (int i = tid; i < rows * CH; i += UM_THREADS) {
-      const int r = i / CH, c = i % CH;
-      cp_async16(dst + tile_off(rows, r, c), src + static_cast<int64_t>(row0 + r) * stride + c * 8, r < rows_valid);
-    }
+    const uint32_t d0 = dst + tile_off(rows, lr, lc);
+    const T* s0 = src + static_cast<int64_t>(row0 + lr) * stride + lc * 8;
+#pragma unroll
+    for (int k = 0; k < rows / RSTEP; ++k)
+      cp_async16(d0 + k * (RSTEP * 128), s0 + static_cast<int64_t>(k * RSTEP) * stride, lr + k * RSTEP < rows_valid);
   };
   auto load_k = [&](int j) { load_tile(sK + (j & 1) * KV_BYTES, kg, p.k_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
   auto load_v = [&](int j) { load_tile(sV + (j & 1) * KV_BYTES, vg, p.v_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
@@ -241,9 +252,14 @@ prefill_umma_kernel(const PrefillParams p) {
   float m_ref = 0.f, l = 0.f;
   bool ok = true;
 
+#ifdef PA_DEBUG_PF_TIMING
+  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+#endif
   for (int j = 0; j < n_kv; ++j) {
+    PF_STAMP(0);
     ok = mbar_wait(bar_s, j & 1, p.status) && ok;
     tc_fence_after();
+    PF_STAMP(1);
     // S_j is complete and so is every MMA before it: K buffer j & 1 and V buffer (j + 1) & 1 are free.
     if (j + 2 < n_kv) load_k(j + 2);
     if (j + 1 < n_kv) load_v(j + 1);
@@ -262,12 +278,17 @@ prefill_umma_kernel(const PrefillParams p) {
         s[32 + i] = __uint_as_float(hi[i]);
       }
     }
+    PF_STAMP(2);
     const int col0 = j * UM_BN;
     const bool plain = !capped && slope == 0.f && scale_log2 > 0.f && col0 + UM_BN <= q0 + 1 && col0 + UM_BN <= len;
     float mx = -INFINITY;
     if (plain) {                               // no mask, no bias: scale folded into the exponent's FMA
+      float m8[8];
 #pragma unroll
-      for (int i = 0; i < UM_BN; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < 8; ++i) m8[i] = s[i];
+#pragma unroll
+      for (int i = 8; i < UM_BN; ++i) m8[i & 7] = fmaxf(m8[i & 7], s[i]);   // eight independent chains
+      mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
       mx *= scale_log2;
     } else {
 #pragma unroll
@@ -293,23 +314,23 @@ prefill_umma_kernel(const PrefillParams p) {
       grow = true;
     }
     uint32_t pk[32];
-    float sum = 0.f;
+    float sum4[4] = {0.f, 0.f, 0.f, 0.f};      // independent chains: two warps per scheduler hide little latency
     if (plain) {
 #pragma unroll
       for (int i = 0; i < UM_BN; i += 2) {
         const float a = exp2_approx(fmaf(s[i], scale_log2, -m_ref)), b = exp2_approx(fmaf(s[i + 1], scale_log2, -m_ref));
-        sum += a + b;
+        sum4[(i >> 1) & 3] += a + b;
         pk[i >> 1] = pack2<T>(a, b);
       }
     } else {
 #pragma unroll
       for (int i = 0; i < UM_BN; i += 2) {
         const float a = exp2_approx(s[i] - m_ref), b = exp2_approx(s[i + 1] - m_ref);
-        sum += a + b;
+        sum4[(i >> 1) & 3] += a + b;
         pk[i >> 1] = pack2<T>(a, b);
       }
     }
-    l = l * corr + sum;
+    l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
     if (__any_sync(0xffffffffu, grow)) {       // warp-uniform: tcgen05.ld / st are warp-wide
 #pragma unroll
       for (int c = 0; c < HEAD; c += 32) {
@@ -321,18 +342,23 @@ prefill_umma_kernel(const PrefillParams p) {
         tmem_st32(tm_lane + COL_O + c, o);
       }
     }
+    PF_STAMP(3);
     tmem_st32(tm_lane + COL_P, pk);
     tmem_st_wait();
+    PF_STAMP(4);
     cp_async_wait<1>();                        // V_j and K_{j+1} have landed (this thread's part)
     fence_proxy_async();
     tc_fence_before();
+    PF_STAMP(5);
     if (!__syncthreads_and(ok)) { ok = false; break; }
+    PF_STAMP(6);
     if (tid == 0) {
       tc_fence_after();
       issue_o(j, j + 1 == n_kv);
       if (j + 1 < n_kv) issue_s(j + 1);
     }
     __syncwarp();
+    PF_STAMP(7);
   }
 
   if (ok) ok = mbar_wait(bar_o, 0, p.status);
@@ -391,6 +417,12 @@ int launch_umma(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef PA_DEBUG_PF_TIMING
+extern "C" int pa_debug_prefill_timing(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_pf_timing, sizeof(g_pf_timing)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int launch_prefill_umma(const PrefillParams& p, int num_seqs, int head_size, uint32_t dtype, cudaStream_t stream) {
   if (dtype == DT_BF16) {

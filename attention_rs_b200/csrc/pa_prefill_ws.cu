@@ -1,0 +1,603 @@
+// Causal self-attention over packed variable-length prompts: the warp-specialised tcgen05 kernel.
+// Same function as the kernels in pa_prefill.cu / pa_prefill_umma.cu (a restatement of src/lib.rs:87-213 of
+// the reference); this is the one that runs for head sizes 64 and 128.
+//
+// One CTA = 256 query rows of one (sequence, head) = two row groups of 128, each with its own S and O
+// accumulators in tensor memory.  Ten warps:
+//   warps 0-3 / 4-7  softmax of group 0 / 1: thread t owns row t of its group (= tensor-memory lane t); reads its
+//                    row of S with tcgen05.ld, writes P (16-bit) over the same columns with tcgen05.st
+//   warp 8           producer: one lane issues the TMA loads (Q once, then K / V tiles of 64 keys into two
+//                    four-deep rings; 128-byte swizzle, the layout the MMA descriptors name)
+//   warps 9 / 10     one lane each issues S = Q K^T of group 0 / 1 (warp 9 owns the tensor-memory allocation)
+//   warps 11 / 12    one lane each issues O += P V of group 0 / 1
+// S of each group is double-buffered, so S_{j+1} = Q K_{j+1}^T is computed while the group's softmax works on
+// S_j, and the two groups share the tensor pipe: MMA latency is off the softmax's critical path.  The issuers
+// are ordered among themselves by barriers only: S_j may overwrite its buffer when P V of tile j - 2 is complete
+// (o_buf), P V of tile j starts when P_j has been written (p_full).
+// O is rescaled only when a row maximum outgrows the reference value of the exponentials by more than 2^8
+// (the result does not depend on that reference); the rescale first waits for the group's last P V.
+//
+// Handshakes (mbarriers): q_full, k_full and v_full per ring slot (TMA bytes), k_empty / v_empty per (group, slot)
+// (tcgen05.commit behind the group's MMAs that read the slot),
+// s_full per (group, buffer) (commit), p_full per (group, buffer) (128 thread arrivals), o_buf per (group, buffer)
+// (commit after P V of a tile: the buffer's P has been read, and O holds the tile), o_last per group (commit after
+// the last P V).  No waiter is ever more than one phase behind its barrier, which a parity wait could not tell:
+// that is why these barriers are split by buffer (tile j + 2 cannot reach a barrier before tile j was consumed).
+// K / V rows past the end of a sequence belong to the next sequence (or are zero past the end of the tensor):
+// their S columns are masked; the V rows of the last, ragged tile are overwritten with zeros by the producer warp
+// before the MMA may use them (v_fixed), so that no value of another sequence can reach the output.
+// Every wait is bounded; a role that gives up records it in the device status word and leaves its loop, which
+// lets the others run into their own limits, and the CTA frees its tensor memory before it returns.
+#include "pa_common.cuh"
+#include "pa_launch.h"
+#include "pa_prefill.h"
+
+#include <cuda.h>
+
+#include <type_traits>
+
+namespace pa {
+namespace {
+
+constexpr int WS_BN = 64;          // keys per tile
+constexpr int WS_GROUP = 128;      // query rows per group = tensor-memory lanes
+constexpr int WS_BM = 2 * WS_GROUP;
+constexpr int WS_STAGES = 4;       // ring depth of K and of V
+constexpr int WS_THREADS = 416;
+constexpr float WS_RESCALE_GAP = 8.0f;
+
+// ---------------------------------------------------------------- PTX wrappers
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Non-blocking probe (mbarrier.try_wait may park the thread inside the memory pipe for a while).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.relaxed.cta.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_nb(uint32_t bar, uint32_t parity, unsigned* status) {
+  for (int it = 0; it < kWaitLimit; ++it) {
+    if (mbar_test(bar, parity)) return true;
+  }
+  atomicOr(status, ST_WAIT_TIMEOUT);
+  return false;
+}
+// Bounded wait for a whole warp: one lane polls (with a pause between probes), the others wait at the warp
+// barrier.  Hundreds of threads polling an mbarrier keep the shared-memory pipe busy that also feeds the MMA
+// operands; with this form the MMAs run at their full rate.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, unsigned* status) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) {
+    ok = false;
+    for (int it = 0; it < kWaitLimit; ++it) {
+      if (mbar_test(bar, parity)) { ok = true; break; }
+      __nanosleep(64);
+    }
+    if (!ok) atomicOr(status, ST_WAIT_TIMEOUT);
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+// The wait names the registers as read-write operands so that no use of them can be scheduled before it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                 "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                 "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: start address >> 4 in bits [0,14), leading byte offset >> 4 in [16,30), stride
+// byte offset >> 4 in [32,46), descriptor version 1 in [46,48), layout 2 = 128-byte swizzle in [61,64).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: D format f32 (bits [4,6) = 1), A / B format in [7,10) / [10,13)
+// (0 = f16, 1 = bf16), B MN-major flag in bit 16, N / 8 in [17,23), M / 16 in [24,29).
+template <typename T>
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
+  const uint32_t fmt = std::is_same<T, __half>::value ? 0u : 1u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+template <int HEAD>
+struct WsLayout {
+  static constexpr int DB = HEAD / 64;                    // 64-element column blocks per row
+  static constexpr int Q_BYTES = WS_GROUP * HEAD * 2;     // one group's Q tile: DB blocks of [128 rows][128 bytes]
+  static constexpr int KV_BYTES = WS_BN * HEAD * 2;       // one K or V tile: DB blocks of [64 rows][128 bytes]
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + WS_STAGES * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + WS_STAGES * KV_BYTES;
+  // barrier slots (8 bytes each)
+  static constexpr int B_Q_FULL = 0;
+  static constexpr int B_K_FULL = 1;
+  static constexpr int B_K_EMPTY = B_K_FULL + WS_STAGES;       // [group][slot]
+  static constexpr int B_V_FULL = B_K_EMPTY + 2 * WS_STAGES;
+  static constexpr int B_V_EMPTY = B_V_FULL + WS_STAGES;       // [group][slot]
+  static constexpr int B_S_FULL = B_V_EMPTY + 2 * WS_STAGES;   // [group][buffer]
+  static constexpr int B_P_FULL = B_S_FULL + 4;                // [group][buffer]
+  static constexpr int B_O_BUF = B_P_FULL + 4;                 // [group][buffer]
+  static constexpr int B_O_LAST = B_O_BUF + 4;                 // [group]
+  static constexpr int B_V_FIXED = B_O_LAST + 2;
+  static constexpr int NUM_BARS = B_V_FIXED + 1;
+  static constexpr int OFF_SLOT = OFF_BAR + NUM_BARS * 8;
+#ifdef PA_DEBUG_PF_TIMING
+  static constexpr int OFF_DBG = OFF_SLOT + 16;
+  static constexpr int BYTES = OFF_DBG + 3 * 64 * 8 * 8 + 1024;
+#else
+  static constexpr int BYTES = OFF_SLOT + 16 + 1024;      // + slack to align the base to 1024
+#endif
+  // tensor-memory columns
+  static constexpr uint32_t COL_O = 0;                    // [group] HEAD columns each
+  static constexpr uint32_t COL_S = 2 * HEAD;             // [group][buffer] 64 columns each; P overwrites the first 32
+  static constexpr uint32_t TM_COLS = 512;
+};
+
+#ifdef PA_DEBUG_PF_TIMING
+__device__ long long g_ws_timing[3 * 64 * 8];
+__device__ long long g_ws_fine[64 * 16];   // [role: softmax 0, softmax 1, mma][iteration][stamp]
+#define WS_STAMP(role, k) do { if (dbg && j < 64) dbg_stamps[((role) * 64 + j) * 8 + (k)] = clock64(); } while (0)
+#else
+#define WS_STAMP(role, k) do { } while (0)
+#endif
+
+template <typename T, int HEAD>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v) {
+  using L = WsLayout<HEAD>;
+  constexpr uint32_t IDESC_S = instr_desc<T>(WS_GROUP, WS_BN, false);
+  constexpr uint32_t IDESC_O = instr_desc<T>(WS_GROUP, HEAD, true);
+  static_assert(HEAD == 64 || HEAD == 128, "tensor-memory budget and descriptors are laid out for these head sizes");
+
+  const int seq = blockIdx.y, head = blockIdx.z;
+  const int tok_lo = static_cast<int>(p.cu_seqlens[seq]), tok_hi = static_cast<int>(p.cu_seqlens[seq + 1]);
+  const int len = tok_hi - tok_lo;
+  const int ntiles = (len + WS_BM - 1) / WS_BM;
+  const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // heaviest (last) tiles first
+  if (qt >= ntiles) return;                     // before any tensor memory is taken
+  const int kvh = head / (p.num_heads / p.num_kv_heads);
+  const int q0 = qt * WS_BM;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef PA_DEBUG_PF_TIMING
+  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9 || warp == 8 || warp == 11);
+#endif
+  const int n_all = (len + WS_BN - 1) / WS_BN;
+  // key tiles each group needs (causal: up to its last row); a group whose rows all lie past the end needs none
+  const int n0 = min((q0 + WS_GROUP + WS_BN - 1) / WS_BN, n_all);
+  const int n1 = q0 + WS_GROUP < len ? min((q0 + WS_BM + WS_BN - 1) / WS_BN, n_all) : 0;
+  const int n_max = max(n0, n1);
+  const bool ragged = n_max == n_all && len % WS_BN != 0;   // the last tile this CTA reads runs past the sequence
+
+  extern __shared__ unsigned char ws_smem_raw[];
+  const uint32_t smem0 = (smem_addr(ws_smem_raw) + 1023u) & ~1023u;   // swizzle atoms are 1024-byte aligned
+  unsigned char* smem = ws_smem_raw + (smem0 - smem_addr(ws_smem_raw));
+  const uint32_t sQ = smem0 + L::OFF_Q, sK = smem0 + L::OFF_K, sV = smem0 + L::OFF_V;
+  auto bar = [&](int idx) { return smem0 + L::OFF_BAR + idx * 8; };
+#ifdef PA_DEBUG_PF_TIMING
+  long long* dbg_stamps = reinterpret_cast<long long*>(smem + L::OFF_DBG);
+  const bool dbg_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  if (dbg_cta) for (int i = threadIdx.x; i < 3 * 64 * 8; i += blockDim.x) dbg_stamps[i] = 0;
+#endif
+
+  if (warp == 9) {
+    if (lane == 0) {
+      for (int i = 0; i < L::NUM_BARS; ++i) mbar_init(bar(i), (i >= L::B_P_FULL && i < L::B_P_FULL + 4) ? WS_GROUP : 1);
+      mbar_init_fence();
+    }
+    __syncwarp();
+    tmem_alloc(smem0 + L::OFF_SLOT, L::TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm_base = *reinterpret_cast<volatile uint32_t*>(smem + L::OFF_SLOT);
+
+  if (warp == 8) {
+    // ================================================================ producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(bar(L::B_Q_FULL), (n1 > 0 ? 2 : 1) * L::Q_BYTES);
+      for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
+        for (int db = 0; db < L::DB; ++db)
+          tma_load_3d(sQ + t * L::Q_BYTES + db * (WS_GROUP * 128), &map_q, db * 64, head, tok_lo + q0 + t * WS_GROUP,
+                      bar(L::B_Q_FULL));
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % WS_STAGES;
+        const uint32_t par = ((j / WS_STAGES) - 1) & 1;   // parity of the slot's previous release
+        if (j >= WS_STAGES) {                             // both groups' S of the tile this one replaces
+          if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_K_EMPTY + s), par, p.status);
+          if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_K_EMPTY + WS_STAGES + s), par, p.status);
+        }
+        if (!ok) break;
+        mbar_expect_tx(bar(L::B_K_FULL + s), L::KV_BYTES);
+        for (int db = 0; db < L::DB; ++db)
+          tma_load_3d(sK + s * L::KV_BYTES + db * (WS_BN * 128), &map_k, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_K_FULL + s));
+        if (j >= WS_STAGES) {
+          if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_V_EMPTY + s), par, p.status);
+          if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_V_EMPTY + WS_STAGES + s), par, p.status);
+        }
+        if (!ok) break;
+        mbar_expect_tx(bar(L::B_V_FULL + s), L::KV_BYTES);
+        for (int db = 0; db < L::DB; ++db)
+          tma_load_3d(sV + s * L::KV_BYTES + db * (WS_BN * 128), &map_v, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_V_FULL + s));
+      }
+    }
+    __syncwarp();
+    if (ragged) {
+      // Zero the V rows of the last tile that lie past the end of the sequence (whole 128-byte rows: the swizzle
+      // only permutes chunks within a row), then let the MMA warp use the tile.
+      const int jl = n_max - 1, s = jl % WS_STAGES;
+      const bool ok = mbar_wait_warp(bar(L::B_V_FULL + s), (jl / WS_STAGES) & 1, p.status);
+      const int r0 = len - jl * WS_BN;            // first row to clear, 1..63
+      if (ok) {
+        const int chunks = (WS_BN - r0) * 8;      // 16-byte chunks per column block
+        for (int db = 0; db < L::DB; ++db) {
+          uint4* base = reinterpret_cast<uint4*>(smem + L::OFF_V + s * L::KV_BYTES + db * (WS_BN * 128) + r0 * 128);
+          for (int i = lane; i < chunks; i += 32) base[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async();
+      }
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(bar(L::B_V_FIXED));
+    }
+  } else if (warp >= 9) {
+    // ================================================================ MMA issue: warps 9 / 10 issue S of group 0 / 1,
+    // warps 11 / 12 issue P V of group 0 / 1.  Four issuers because issuing is what limits one: the pipe executes a
+    // 128 x 64 x 16 MMA in about 50 clocks, a lone issuing thread beside busy softmax warps needs twice that.
+    // Descriptors are built once; a tile, a column block or a k-step is a constant added to the address field
+    // (16-byte units; shared memory ends below 2^18 bytes, so the 14-bit field never carries).
+    const int t = (warp - 9) & 1;
+    const int nt = t == 0 ? n0 : n1;
+    if (lane == 0 && warp < 11) {
+      // ---- S_j = Q_t K_j^T -> buffer j & 1: HEAD / 16 MMAs of K = 16 (32 bytes along the swizzled rows)
+      bool ok = mbar_wait_nb(bar(L::B_Q_FULL), 0, p.status);
+      const uint64_t a0 = smem_desc(sQ + t * L::Q_BYTES, 16, 1024), dk0 = smem_desc(sK, 16, 1024);
+      for (int j = 0; j < nt && ok; ++j) {
+        const int slot = j % WS_STAGES;
+        WS_STAMP(2, 0);
+        ok = mbar_wait_nb(bar(L::B_K_FULL + slot), (j / WS_STAGES) & 1, p.status);
+        WS_STAMP(2, 1);
+        // the buffer still holds P of tile j - 2 until that tile's P V is complete
+        if (ok && j >= 2) ok = mbar_wait_nb(bar(L::B_O_BUF + t * 2 + (j & 1)), ((j - 2) >> 1) & 1, p.status);
+        if (!ok) break;
+        WS_STAMP(2, 2);
+        tc_fence_after();
+        const uint64_t b0 = dk0 + static_cast<uint32_t>((slot * L::KV_BYTES) >> 4);
+        const uint32_t d = tm_base + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
+#pragma unroll
+        for (int ks = 0; ks < HEAD / 16; ++ks)
+          umma_ss(d, a0 + (((ks >> 2) * (WS_GROUP * 128) + (ks & 3) * 32) >> 4), b0 + (((ks >> 2) * (WS_BN * 128) + (ks & 3) * 32) >> 4),
+                  IDESC_S, ks > 0);
+        WS_STAMP(2, 3);
+        tc_commit(bar(L::B_S_FULL + t * 2 + (j & 1)));
+        tc_commit(bar(L::B_K_EMPTY + t * WS_STAGES + slot));
+        WS_STAMP(2, 4);
+      }
+    } else if (lane == 0) {
+      // ---- O_t (+)= P_j V_j: 4 MMAs of K = 16 keys (two 8-key groups = 2048 bytes of the MN-major tile); P sits in the
+      // first 32 columns of the S buffer it was computed from
+      bool ok = true;
+      const uint64_t dv0 = smem_desc(sV, WS_BN * 128, 1024);
+      const uint32_t d = tm_base + L::COL_O + t * HEAD;
+      for (int j = 0; j < nt && ok; ++j) {
+        const int slot = j % WS_STAGES;
+        WS_STAMP(2, 5);
+        ok = mbar_wait_nb(bar(L::B_P_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
+        if (ok) ok = mbar_wait_nb(bar(L::B_V_FULL + slot), (j / WS_STAGES) & 1, p.status);
+        if (ok && ragged && j == n_all - 1) ok = mbar_wait_nb(bar(L::B_V_FIXED), 0, p.status);
+        if (!ok) break;
+        WS_STAMP(2, 6);
+        tc_fence_after();
+        const uint64_t b0 = dv0 + static_cast<uint32_t>((slot * L::KV_BYTES) >> 4);
+        const uint32_t pcol = tm_base + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
+#pragma unroll
+        for (int kk = 0; kk < WS_BN / 16; ++kk) umma_ts(d, pcol + kk * 8, b0 + ((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(bar(L::B_O_BUF + t * 2 + (j & 1)));
+        tc_commit(bar(L::B_V_EMPTY + t * WS_STAGES + slot));
+        if (j + 1 == nt) tc_commit(bar(L::B_O_LAST + t));
+        WS_STAMP(2, 7);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================================================================ softmax, one thread per query row
+    const int t = warp >> 2;
+    const int nt = t == 0 ? n0 : n1;
+    const int row = q0 + t * WS_GROUP + (tid & (WS_GROUP - 1));   // query position within the sequence
+    const uint32_t tm_lane = tm_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t tm_o = tm_lane + L::COL_O + t * HEAD;
+    const float slope = p.alibi_slopes ? p.alibi_slopes[head] * LOG2E : 0.f;
+    const bool capped = p.softcap != 1.0f;
+    const float scale_log2 = p.scale * LOG2E;
+    float m_ref = 0.f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nt; ++j) {
+      const uint32_t tm_s = tm_lane + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
+      WS_STAMP(t, 0);
+      ok = mbar_wait_warp(bar(L::B_S_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
+      if (!ok) break;
+      tc_fence_after();
+      WS_STAMP(t, 1);
+      float s[WS_BN];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(tm_s, lo);
+        tmem_ld32(tm_s + 32, hi);
+        tmem_ld_wait(lo);
+        tmem_ld_wait(hi);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(lo[i]);
+          s[32 + i] = __uint_as_float(hi[i]);
+        }
+      }
+      WS_STAMP(t, 2);
+      const int col0 = j * WS_BN;
+      // no masked element for any row of the group, no bias: the scale is folded into the exponent's FMA
+      const bool plain = !capped && slope == 0.f && scale_log2 > 0.f && col0 + WS_BN <= q0 + t * WS_GROUP + 1 && col0 + WS_BN <= len;
+      float mx;
+      if (plain) {
+        float m8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m8[i] = s[i];
+#pragma unroll
+        for (int i = 8; i < WS_BN; ++i) m8[i & 7] = fmaxf(m8[i & 7], s[i]);   // eight independent chains
+        mx = fmaxf(fmaxf(fmaxf(m8[0], m8[1]), fmaxf(m8[2], m8[3])), fmaxf(fmaxf(m8[4], m8[5]), fmaxf(m8[6], m8[7])));
+        mx *= scale_log2;
+      } else {
+        mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < WS_BN; ++i) {
+          const int col = col0 + i;
+          float x = s[i];
+          if (capped) x = tanh_approx(x * p.scale / p.softcap) * p.softcap * LOG2E;
+          else x *= scale_log2;
+          x += slope * static_cast<float>(col - row);
+          if (col >= len || col > row) x = -INFINITY;
+          s[i] = x;
+          mx = fmaxf(mx, x);
+        }
+      }
+      // Reference value of the exponentials.  Tile 0 always holds key 0, which no row masks, so mx is finite there.
+      float corr = 1.f;
+      bool grow = false;
+      if (j == 0) {
+        m_ref = mx;
+      } else if (mx > m_ref + WS_RESCALE_GAP) {
+        corr = exp2_approx(m_ref - mx);
+        m_ref = mx;
+        grow = true;
+      }
+      uint32_t pk[32];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (plain) {
+#pragma unroll
+        for (int i = 0; i < WS_BN; i += 2) {
+          const float a = exp2_approx(fmaf(s[i], scale_log2, -m_ref)), b = exp2_approx(fmaf(s[i + 1], scale_log2, -m_ref));
+          sum4[(i >> 1) & 3] += a + b;
+          pk[i >> 1] = pack2<T>(a, b);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < WS_BN; i += 2) {
+          const float a = exp2_approx(s[i] - m_ref), b = exp2_approx(s[i + 1] - m_ref);
+          sum4[(i >> 1) & 3] += a + b;
+          pk[i >> 1] = pack2<T>(a, b);
+        }
+      }
+      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      WS_STAMP(t, 5);
+      if (__any_sync(0xffffffffu, grow)) {       // warp-uniform: tcgen05.ld / st are warp-wide
+        // O still receives P V of tile j - 1 (grow implies j > 0) until that tile's o_buf says otherwise
+        ok = mbar_wait_warp(bar(L::B_O_BUF + t * 2 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HEAD; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tm_o + c, o);
+          tmem_ld_wait(o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st32(tm_o + c, o);
+        }
+      }
+      WS_STAMP(t, 3);
+      tmem_st32(tm_s, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bar(L::B_P_FULL + t * 2 + (j & 1)));
+      WS_STAMP(t, 4);
+    }
+    if (nt > 0) {
+      // A barrier of its own for the end: a parity wait on o_done could be two phases behind here and pass early.
+      if (ok) ok = mbar_wait_warp(bar(L::B_O_LAST + t), 0, p.status);
+      tc_fence_after();
+      if (ok) {
+        // ---- normalise and store this thread's row (rows past the end only take part in the warp-wide loads)
+        const float inv = 1.0f / l;
+        T* og = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + row) * p.o_stride + head * HEAD;
+        const bool wide = reinterpret_cast<uintptr_t>(og) % 16 == 0;
+#pragma unroll
+        for (int c = 0; c < HEAD; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tm_o + c, o);
+          tmem_ld_wait(o);
+          if (row < len) {
+            if (wide) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 w;
+                w.x = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                w.y = pack2<T>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                w.z = pack2<T>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                w.w = pack2<T>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                *reinterpret_cast<uint4*>(og + c + i) = w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 2)
+                *reinterpret_cast<uint32_t*>(og + c + i) = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+#ifdef PA_DEBUG_PF_TIMING
+  if (dbg_cta) for (int i = threadIdx.x; i < 3 * 64 * 8; i += blockDim.x) g_ws_timing[i] = dbg_stamps[i];
+#endif
+  if (warp == 9) tmem_dealloc(tm_base, L::TM_COLS);
+}
+
+// ---------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// [tokens, heads, HEAD] with a token stride: a 3-D map (d, head, token); one box = 64 elements of one head for
+// box_rows tokens, written to shared memory as rows of 128 bytes with the 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, uint32_t dtype, int head_size, int heads, int64_t tokens, int64_t token_stride,
+              int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_size), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_size) * 2, static_cast<cuuint64_t>(token_stride) * 2};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base),
+            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int HEAD>
+int launch_ws(const PrefillParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int num_seqs,
+              cudaStream_t stream) {
+  auto kernel = prefill_ws_kernel<T, HEAD>;
+  constexpr int smem = WsLayout<HEAD>::BYTES;
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return PA_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return PA_ERR_CUDA;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const dim3 grid((p.max_seqlen + WS_BM - 1) / WS_BM, num_seqs, p.num_heads);
+  kernel<<<grid, WS_THREADS, smem, stream>>>(p, mq, mk, mv);
+  return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
+}
+
+}  // namespace
+
+#ifdef PA_DEBUG_PF_TIMING
+extern "C" int pa_debug_prefill_ws_timing(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_ws_timing, sizeof(g_ws_timing)) == cudaSuccess ? 0 : 1;
+}
+extern "C" int pa_debug_prefill_ws_fine(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, g_ws_fine, sizeof(g_ws_fine)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
+int launch_prefill_ws(const PrefillParams& p, int num_seqs, int total_tokens, int head_size, uint32_t dtype, cudaStream_t stream) {
+  if ((dtype != DT_BF16 && dtype != DT_F16) || (head_size != 64 && head_size != 128)) return PA_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  if (!make_map(&mq, p.q, dtype, head_size, p.num_heads, total_tokens, p.q_stride, WS_GROUP) ||
+      !make_map(&mk, p.k, dtype, head_size, p.num_kv_heads, total_tokens, p.k_stride, WS_BN) ||
+      !make_map(&mv, p.v, dtype, head_size, p.num_kv_heads, total_tokens, p.v_stride, WS_BN))
+    return PA_ERR_UNSUPPORTED;
+  if (dtype == DT_BF16)
+    return head_size == 64 ? launch_ws<__nv_bfloat16, 64>(p, mq, mk, mv, num_seqs, stream)
+                           : launch_ws<__nv_bfloat16, 128>(p, mq, mk, mv, num_seqs, stream);
+  return head_size == 64 ? launch_ws<__half, 64>(p, mq, mk, mv, num_seqs, stream) : launch_ws<__half, 128>(p, mq, mk, mv, num_seqs, stream);
+}
+
+}  // namespace pa

@@ -74,7 +74,7 @@ def load_library() -> ctypes.CDLL:
     L.paged_decode_step_v2.restype = ctypes.c_int
     L.paged_decode_step_v2.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp] + tail + [vp, u32, f32, f32, i64]
     L.paged_prefill_attention.restype = ctypes.c_int
-    L.paged_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp, u32, i64]
+    L.paged_prefill_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, vp, u32, i64]
     L.pa_copy_blocks.restype = ctypes.c_int
     L.pa_copy_blocks.argtypes = [vp, vp, vp, i32, i32, i32, i32, i64]
     L.pa_paged_attention_workspace_bytes.restype = ctypes.c_size_t
@@ -274,7 +274,7 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
         if out is None:
             out = torch.empty(q.shape, dtype=q.dtype, device=dev)
         rc = L.paged_prefill_attention(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), cu_seqlens.data_ptr(),
-                                       cu_seqlens.shape[0] - 1, int(max_seqlen), q.shape[1], k.shape[1], q.shape[2],
+                                       cu_seqlens.shape[0] - 1, q.shape[0], int(max_seqlen), q.shape[1], k.shape[1], q.shape[2],
                                        q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(softmax_scale),
                                        float(softcapping), None if alibi_slopes is None else alibi_slopes.data_ptr(),
                                        dtype_code(q), torch.cuda.current_stream(dev).cuda_stream)

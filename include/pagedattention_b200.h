@@ -162,11 +162,14 @@ int paged_decode_step_v2(void* out, float* exp_sums, float* max_logits, void* tm
  * else per-sequence matmul / soft-cap / causal mask / f32 softmax / matmul, with kv heads repeated for grouped
  * queries).  query / out: [total_tokens, num_heads, head_size]; key / value: [total_tokens, num_kv_heads,
  * head_size]; token strides q_stride / k_stride / v_stride / out_stride in elements; cu_seqlens: u32
- * [num_seqs + 1] prefix sums of the prompt lengths (device memory); max_seqlen: the longest prompt.
+ * [num_seqs + 1] prefix sums of the prompt lengths (device memory); total_tokens: rows of query / key / value
+ * (= cu_seqlens[num_seqs], which the host must pass because the TMA descriptors carry the extent);
+ * max_seqlen: the longest prompt.
  * f16 / bf16, head_size 64 / 128 / 256.  alibi_slopes may be NULL; softcapping == 1.0 disables the soft-cap.
  * Writing the prompt's keys and values into the paged cache stays a call of call_reshape_and_cache. */
 int paged_prefill_attention(void* out, const void* query, const void* key, const void* value,
-                            const uint32_t* cu_seqlens, int32_t num_seqs, int32_t max_seqlen, int32_t num_heads,
+                            const uint32_t* cu_seqlens, int32_t num_seqs, int32_t total_tokens, int32_t max_seqlen,
+                            int32_t num_heads,
                             int32_t num_kv_heads, int32_t head_size, int32_t q_stride, int32_t k_stride,
                             int32_t v_stride, int32_t out_stride, float scale, float softcapping,
                             const float* alibi_slopes, uint32_t dtype, int64_t stream);

@@ -10,14 +10,15 @@ from tests.helpers import DT, from_torch_f32, to_torch, tolerances
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["tcgen05", "warp_mma"])
+@pytest.fixture(params=["tcgen05", "tcgen05_simple", "warp_mma"])
 def kernel(request, monkeypatch):
-    """Head sizes 64 and 128 run on the tcgen05 kernel; PA_PREFILL_WARP_MMA=1 sends them to the warp-level MMA
-    kernel, which head size 256 always uses.  The library reads the variable per call."""
-    if request.param == "warp_mma":
-        monkeypatch.setenv("PA_PREFILL_WARP_MMA", "1")
+    """Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel; PA_PREFILL_KERNEL sends them to the
+    single-group tcgen05 kernel or to the warp-level MMA kernel, which head size 256 always uses.  The library
+    reads the variable per call."""
+    if request.param == "tcgen05":
+        monkeypatch.delenv("PA_PREFILL_KERNEL", raising=False)
     else:
-        monkeypatch.delenv("PA_PREFILL_WARP_MMA", raising=False)
+        monkeypatch.setenv("PA_PREFILL_KERNEL", request.param)
     return request.param
 
 
@@ -66,6 +67,8 @@ def test_prefill_variants(kernel):
     run([512, 130], 2, 1, 128, "bf16", seed=7, key_growth=1 / 32)   # accumulator rescaled again and again
     run([700], 2, 2, 64, "f16", seed=8, key_growth=1 / 64)
     run([1, 1, 2, 0, 3], 2, 1, 128, "bf16", seed=9)                 # tiny and empty prompts
+    run([1100, 257, 255, 384], 4, 1, 128, "bf16", seed=10)          # more key tiles than ring slots, ragged ends
+    run([640, 129], 4, 4, 64, "f16", seed=11)
 
 
 def test_prefill_rejects_unsupported():
