@@ -135,13 +135,6 @@ __device__ __forceinline__ uint32_t tile_off(int rows, int r, int c) {
   return static_cast<uint32_t>((c >> 3) * (rows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
-#ifdef PA_DEBUG_PF_TIMING
-__device__ long long g_pf_timing[64 * 8];
-#define PF_STAMP(k) do { if (dbg && j < 64) g_pf_timing[j * 8 + (k)] = clock64(); } while (0)
-#else
-#define PF_STAMP(k) do { } while (0)
-#endif
-
 template <typename T, int HEAD>
 __global__ void __launch_bounds__(UM_THREADS)
 prefill_umma_kernel(const PrefillParams p) {
@@ -252,14 +245,9 @@ prefill_umma_kernel(const PrefillParams p) {
   float m_ref = 0.f, l = 0.f;
   bool ok = true;
 
-#ifdef PA_DEBUG_PF_TIMING
-  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
-#endif
   for (int j = 0; j < n_kv; ++j) {
-    PF_STAMP(0);
     ok = mbar_wait(bar_s, j & 1, p.status) && ok;
     tc_fence_after();
-    PF_STAMP(1);
     // S_j is complete and so is every MMA before it: K buffer j & 1 and V buffer (j + 1) & 1 are free.
     if (j + 2 < n_kv) load_k(j + 2);
     if (j + 1 < n_kv) load_v(j + 1);
@@ -278,7 +266,6 @@ prefill_umma_kernel(const PrefillParams p) {
         s[32 + i] = __uint_as_float(hi[i]);
       }
     }
-    PF_STAMP(2);
     const int col0 = j * UM_BN;
     const bool plain = !capped && slope == 0.f && scale_log2 > 0.f && col0 + UM_BN <= q0 + 1 && col0 + UM_BN <= len;
     float mx = -INFINITY;
@@ -342,23 +329,18 @@ prefill_umma_kernel(const PrefillParams p) {
         tmem_st32(tm_lane + COL_O + c, o);
       }
     }
-    PF_STAMP(3);
     tmem_st32(tm_lane + COL_P, pk);
     tmem_st_wait();
-    PF_STAMP(4);
     cp_async_wait<1>();                        // V_j and K_{j+1} have landed (this thread's part)
     fence_proxy_async();
     tc_fence_before();
-    PF_STAMP(5);
     if (!__syncthreads_and(ok)) { ok = false; break; }
-    PF_STAMP(6);
     if (tid == 0) {
       tc_fence_after();
       issue_o(j, j + 1 == n_kv);
       if (j + 1 < n_kv) issue_s(j + 1);
     }
     __syncwarp();
-    PF_STAMP(7);
   }
 
   if (ok) ok = mbar_wait(bar_o, 0, p.status);
@@ -417,12 +399,6 @@ int launch_umma(const PrefillParams& p, int num_seqs, cudaStream_t stream) {
 }
 
 }  // namespace
-
-#ifdef PA_DEBUG_PF_TIMING
-extern "C" int pa_debug_prefill_timing(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_pf_timing, sizeof(g_pf_timing)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int launch_prefill_umma(const PrefillParams& p, int num_seqs, int head_size, uint32_t dtype, cudaStream_t stream) {
   if (dtype == DT_BF16) {

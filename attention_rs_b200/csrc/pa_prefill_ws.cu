@@ -8,20 +8,18 @@
 //                    row of S with tcgen05.ld, writes P (16-bit) over the same columns with tcgen05.st
 //   warp 8           producer: one lane issues the TMA loads (Q once, then K / V tiles of 64 keys into two
 //                    four-deep rings; 128-byte swizzle, the layout the MMA descriptors name)
-//   warps 9 / 10     one lane each issues S = Q K^T of group 0 / 1 (warp 9 owns the tensor-memory allocation)
-//   warps 11 / 12    one lane each issues O += P V of group 0 / 1
-// S of each group is double-buffered, so S_{j+1} = Q K_{j+1}^T is computed while the group's softmax works on
-// S_j, and the two groups share the tensor pipe: MMA latency is off the softmax's critical path.  The issuers
-// are ordered among themselves by barriers only: S_j may overwrite its buffer when P V of tile j - 2 is complete
-// (o_buf), P V of tile j starts when P_j has been written (p_full).
+//   warps 9 / 10     one lane each issues the MMAs of group 0 / 1 (warp 9 owns the tensor-memory allocation)
+// S of each group is double-buffered and runs two tiles ahead: as soon as P_j has been written (p_full) the
+// group's issuer sends O += P_j V_j and, directly behind it, S_{j+2} = Q K_{j+2}^T into the buffer that P_j
+// occupies (MMAs of one thread complete in issue order).  MMA latency is off the softmax's critical path, and
+// the two groups share the tensor pipe.
 // O is rescaled only when a row maximum outgrows the reference value of the exponentials by more than 2^8
 // (the result does not depend on that reference); the rescale first waits for the group's last P V.
 //
 // Handshakes (mbarriers): q_full, k_full and v_full per ring slot (TMA bytes), k_empty / v_empty per (group, slot)
 // (tcgen05.commit behind the group's MMAs that read the slot),
-// s_full per (group, buffer) (commit), p_full per (group, buffer) (128 thread arrivals), o_buf per (group, buffer)
-// (commit after P V of a tile: the buffer's P has been read, and O holds the tile), o_last per group (commit after
-// the last P V).  No waiter is ever more than one phase behind its barrier, which a parity wait could not tell:
+// s_full per (group, buffer) (commit), p_full per (group, buffer) (128 thread arrivals), o_last per group (commit
+// after the last P V).  The rare rescale of O waits for P V of the tile before on that tile's v_empty.  No waiter is ever more than one phase behind its barrier, which a parity wait could not tell:
 // that is why these barriers are split by buffer (tile j + 2 cannot reach a barrier before tile j was consumed).
 // K / V rows past the end of a sequence belong to the next sequence (or are zero past the end of the tensor):
 // their S columns are masked; the V rows of the last, ragged tile are overwritten with zeros by the producer warp
@@ -43,7 +41,7 @@ constexpr int WS_BN = 64;          // keys per tile
 constexpr int WS_GROUP = 128;      // query rows per group = tensor-memory lanes
 constexpr int WS_BM = 2 * WS_GROUP;
 constexpr int WS_STAGES = 4;       // ring depth of K and of V
-constexpr int WS_THREADS = 416;
+constexpr int WS_THREADS = 352;
 constexpr float WS_RESCALE_GAP = 8.0f;
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -57,7 +55,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.relaxed.cta.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -155,6 +153,36 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Packed pairs of f32 (two lanes of one 64-bit register): one FMA-pipe instruction does both.
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void up2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) { uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
+// 2^x for a pair on the FMA pipe, to take load off the special-function unit (16 results per clock per SM, the
+// narrowest pipe of this kernel): x = n + r with n = round(x), r in [-0.5, 0.5]; a cubic for 2^r (relative error
+// 8e-5, far below the 16-bit rounding of P) whose exponent field then receives n.  x is clamped so that n stays
+// in the normal range; the magic constant 1.5 * 2^23 leaves n in the low mantissa bits of the sum.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& a, float& b) {
+  constexpr float C0 = 0.9999289512634277f, C1 = 0.6932762265205383f, C2 = 0.24260404706001282f, C3 = 0.05508868396282196f;
+  constexpr float MAGIC = 12582912.f;
+  float x0, x1;
+  up2(x2, x0, x1);
+  const uint64_t xc = pk2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t mg = pk2(MAGIC, MAGIC);
+  const uint64_t fl = add2(xc, mg);
+  const uint64_t r = sub2(xc, sub2(fl, mg));
+  uint64_t q = fma2(pk2(C3, C3), r, pk2(C2, C2));
+  q = fma2(q, r, pk2(C1, C1));
+  q = fma2(q, r, pk2(C0, C0));
+  float q0, q1, f0, f1;
+  up2(q, q0, q1);
+  up2(fl, f0, f1);
+  a = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(f0) << 23));
+  b = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(f1) << 23));
+}
+
 // Shared-memory matrix descriptor: start address >> 4 in bits [0,14), leading byte offset >> 4 in [16,30), stride
 // byte offset >> 4 in [32,46), descriptor version 1 in [46,48), layout 2 = 128-byte swizzle in [61,64).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -163,10 +191,8 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 }
 // Instruction descriptor of kind::f16: D format f32 (bits [4,6) = 1), A / B format in [7,10) / [10,13)
 // (0 = f16, 1 = bf16), B MN-major flag in bit 16, N / 8 in [17,23), M / 16 in [24,29).
-template <typename T>
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
-  const uint32_t fmt = std::is_same<T, __half>::value ? 0u : 1u;
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, uint32_t a_fmt, uint32_t b_fmt, bool b_mn_major) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
@@ -187,8 +213,7 @@ struct WsLayout {
   static constexpr int B_V_EMPTY = B_V_FULL + WS_STAGES;       // [group][slot]
   static constexpr int B_S_FULL = B_V_EMPTY + 2 * WS_STAGES;   // [group][buffer]
   static constexpr int B_P_FULL = B_S_FULL + 4;                // [group][buffer]
-  static constexpr int B_O_BUF = B_P_FULL + 4;                 // [group][buffer]
-  static constexpr int B_O_LAST = B_O_BUF + 4;                 // [group]
+  static constexpr int B_O_LAST = B_P_FULL + 4;                // [group]
   static constexpr int B_V_FIXED = B_O_LAST + 2;
   static constexpr int NUM_BARS = B_V_FIXED + 1;
   static constexpr int OFF_SLOT = OFF_BAR + NUM_BARS * 8;
@@ -205,8 +230,9 @@ struct WsLayout {
 };
 
 #ifdef PA_DEBUG_PF_TIMING
-__device__ long long g_ws_timing[3 * 64 * 8];
-__device__ long long g_ws_fine[64 * 16];   // [role: softmax 0, softmax 1, mma][iteration][stamp]
+// Clock stamps of one CTA (-DPA_DEBUG_PF_TIMING, a tuning build): kept in shared memory while the kernel runs, because
+// a global store in front of a barrier probe delays the probe by hundreds of clocks.
+__device__ long long g_ws_timing[3 * 64 * 8];   // [role: softmax 0, softmax 1, MMA issuer 0][tile][stamp]
 #define WS_STAMP(role, k) do { if (dbg && j < 64) dbg_stamps[((role) * 64 + j) * 8 + (k)] = clock64(); } while (0)
 #else
 #define WS_STAMP(role, k) do { } while (0)
@@ -217,8 +243,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
 prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v) {
   using L = WsLayout<HEAD>;
-  constexpr uint32_t IDESC_S = instr_desc<T>(WS_GROUP, WS_BN, false);
-  constexpr uint32_t IDESC_O = instr_desc<T>(WS_GROUP, HEAD, true);
+  constexpr uint32_t FMT = std::is_same<T, __half>::value ? 0u : 1u;
+  constexpr uint32_t IDESC_S = instr_desc(WS_GROUP, WS_BN, FMT, FMT, false);
+  constexpr uint32_t IDESC_O = instr_desc(WS_GROUP, HEAD, FMT, FMT, true);
   static_assert(HEAD == 64 || HEAD == 128, "tensor-memory budget and descriptors are laid out for these head sizes");
 
   const int seq = blockIdx.y, head = blockIdx.z;
@@ -231,7 +258,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
   const int q0 = qt * WS_BM;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef PA_DEBUG_PF_TIMING
-  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9 || warp == 8 || warp == 11);
+  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9);
 #endif
   const int n_all = (len + WS_BN - 1) / WS_BN;
   // key tiles each group needs (causal: up to its last row); a group whose rows all lie past the end needs none
@@ -314,64 +341,77 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       if (lane == 0 && ok) mbar_arrive(bar(L::B_V_FIXED));
     }
   } else if (warp >= 9) {
-    // ================================================================ MMA issue: warps 9 / 10 issue S of group 0 / 1,
-    // warps 11 / 12 issue P V of group 0 / 1.  Four issuers because issuing is what limits one: the pipe executes a
-    // 128 x 64 x 16 MMA in about 50 clocks, a lone issuing thread beside busy softmax warps needs twice that.
-    // Descriptors are built once; a tile, a column block or a k-step is a constant added to the address field
-    // (16-byte units; shared memory ends below 2^18 bytes, so the 14-bit field never carries).
-    const int t = (warp - 9) & 1;
+    // ================================================================ MMA issue: warp 9 / 10 for group 0 / 1.
+    // Per tile j the lane issues P V of tile j and, directly behind it, S of tile j + 2 into the buffer whose P
+    // that P V reads: MMAs of one thread execute in issue order, so the overwrite needs no barrier, and S runs two
+    // tiles ahead of the softmax.  One issuer per group, because issuing is slow beside busy softmax warps (an
+    // instruction of this warp waits in the same queue as their special-function work); the two groups' issue
+    // streams overlap.  Descriptors are built once; a tile, a column block or a k-step is a constant added to the
+    // address field (16-byte units; shared memory ends below 2^18 bytes, so the 14-bit field never carries).
+    const int t = warp - 9;
     const int nt = t == 0 ? n0 : n1;
-    if (lane == 0 && warp < 11) {
-      // ---- S_j = Q_t K_j^T -> buffer j & 1: HEAD / 16 MMAs of K = 16 (32 bytes along the swizzled rows)
-      bool ok = mbar_wait_nb(bar(L::B_Q_FULL), 0, p.status);
-      const uint64_t a0 = smem_desc(sQ + t * L::Q_BYTES, 16, 1024), dk0 = smem_desc(sK, 16, 1024);
-      for (int j = 0; j < nt && ok; ++j) {
-        const int slot = j % WS_STAGES;
-        WS_STAMP(2, 0);
-        ok = mbar_wait_nb(bar(L::B_K_FULL + slot), (j / WS_STAGES) & 1, p.status);
-        WS_STAMP(2, 1);
-        // the buffer still holds P of tile j - 2 until that tile's P V is complete
-        if (ok && j >= 2) ok = mbar_wait_nb(bar(L::B_O_BUF + t * 2 + (j & 1)), ((j - 2) >> 1) & 1, p.status);
-        if (!ok) break;
-        WS_STAMP(2, 2);
-        tc_fence_after();
-        const uint64_t b0 = dk0 + static_cast<uint32_t>((slot * L::KV_BYTES) >> 4);
-        const uint32_t d = tm_base + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
-#pragma unroll
-        for (int ks = 0; ks < HEAD / 16; ++ks)
-          umma_ss(d, a0 + (((ks >> 2) * (WS_GROUP * 128) + (ks & 3) * 32) >> 4), b0 + (((ks >> 2) * (WS_BN * 128) + (ks & 3) * 32) >> 4),
-                  IDESC_S, ks > 0);
-        WS_STAMP(2, 3);
-        tc_commit(bar(L::B_S_FULL + t * 2 + (j & 1)));
-        tc_commit(bar(L::B_K_EMPTY + t * WS_STAGES + slot));
-        WS_STAMP(2, 4);
+    // A probe of a barrier takes this warp hundreds of clocks (see above), so the barriers one step needs are
+    // probed together: lane i probes the i-th of them with the same instruction, until all have been seen.
+    auto wait4 = [&](uint32_t b0, uint32_t p0, uint32_t b1, uint32_t p1, bool use1, uint32_t b2, uint32_t p2, bool use2, uint32_t b3,
+                     uint32_t p3, bool use3) -> bool {
+      const uint32_t mybar = lane == 0 ? b0 : lane == 1 ? b1 : lane == 2 ? b2 : b3;
+      const uint32_t mypar = lane == 0 ? p0 : lane == 1 ? p1 : lane == 2 ? p2 : p3;
+      bool done = !(lane == 0 || (lane == 1 && use1) || (lane == 2 && use2) || (lane == 3 && use3));
+      for (int it = 0; it < kWaitLimit; ++it) {
+        if (!done) done = mbar_test(mybar, mypar);
+        if (__all_sync(0xffffffffu, done)) return true;
       }
-    } else if (lane == 0) {
-      // ---- O_t (+)= P_j V_j: 4 MMAs of K = 16 keys (two 8-key groups = 2048 bytes of the MN-major tile); P sits in the
-      // first 32 columns of the S buffer it was computed from
-      bool ok = true;
-      const uint64_t dv0 = smem_desc(sV, WS_BN * 128, 1024);
-      const uint32_t d = tm_base + L::COL_O + t * HEAD;
-      for (int j = 0; j < nt && ok; ++j) {
-        const int slot = j % WS_STAGES;
-        WS_STAMP(2, 5);
-        ok = mbar_wait_nb(bar(L::B_P_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
-        if (ok) ok = mbar_wait_nb(bar(L::B_V_FULL + slot), (j / WS_STAGES) & 1, p.status);
-        if (ok && ragged && j == n_all - 1) ok = mbar_wait_nb(bar(L::B_V_FIXED), 0, p.status);
-        if (!ok) break;
-        WS_STAMP(2, 6);
+      if (lane == 0) atomicOr(p.status, ST_WAIT_TIMEOUT);
+      return false;
+    };
+    const uint64_t a0 = smem_desc(sQ + t * L::Q_BYTES, 16, 1024), dk0 = smem_desc(sK, 16, 1024);
+    const uint64_t dv0 = smem_desc(sV, WS_BN * 128, 1024);
+    const uint32_t d_o = tm_base + L::COL_O + t * HEAD;
+    // S_j = Q_t K_j^T -> buffer j & 1: HEAD / 16 MMAs of K = 16 (32 bytes along the swizzled rows)
+    auto issue_s = [&](int j) {
+      const int slot = j % WS_STAGES;
+      const uint64_t b0 = dk0 + static_cast<uint32_t>((slot * L::KV_BYTES) >> 4);
+      const uint32_t d = tm_base + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
+#pragma unroll
+      for (int ks = 0; ks < HEAD / 16; ++ks)
+        umma_ss(d, a0 + (((ks >> 2) * (WS_GROUP * 128) + (ks & 3) * 32) >> 4), b0 + (((ks >> 2) * (WS_BN * 128) + (ks & 3) * 32) >> 4),
+                IDESC_S, ks > 0);
+      tc_commit(bar(L::B_S_FULL + t * 2 + (j & 1)));
+      tc_commit(bar(L::B_K_EMPTY + t * WS_STAGES + slot));
+    };
+    bool ok = nt > 0;
+    if (ok) ok = wait4(bar(L::B_Q_FULL), 0, bar(L::B_K_FULL + 0), 0, true, bar(L::B_K_FULL + 1), 0, nt > 1, 0, 0, false);
+    if (ok && lane == 0) {                               // both buffers are free at the start
+      tc_fence_after();
+      issue_s(0);
+      if (nt > 1) issue_s(1);
+    }
+    __syncwarp();
+    for (int j = 0; j < nt && ok; ++j) {
+      const int slot = j % WS_STAGES;
+      WS_STAMP(2, 0);
+      // P of this tile, its V, the K tile of the S that follows, and on a ragged last tile the producer's clearing
+      ok = wait4(bar(L::B_P_FULL + t * 2 + (j & 1)), (j >> 1) & 1, bar(L::B_V_FULL + slot), (j / WS_STAGES) & 1, true,
+                 bar(L::B_K_FULL + (j + 2) % WS_STAGES), ((j + 2) / WS_STAGES) & 1, j + 2 < nt, bar(L::B_V_FIXED), 0,
+                 ragged && j == n_all - 1);
+      if (!ok) break;
+      WS_STAMP(2, 2);
+      if (lane == 0) {
         tc_fence_after();
+        // O_t (+)= P_j V_j: 4 MMAs of K = 16 keys (two 8-key groups = 2048 bytes of the MN-major tile); P sits in
+        // the first 32 columns of the S buffer it was computed from
         const uint64_t b0 = dv0 + static_cast<uint32_t>((slot * L::KV_BYTES) >> 4);
         const uint32_t pcol = tm_base + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
 #pragma unroll
-        for (int kk = 0; kk < WS_BN / 16; ++kk) umma_ts(d, pcol + kk * 8, b0 + ((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar(L::B_O_BUF + t * 2 + (j & 1)));
-        tc_commit(bar(L::B_V_EMPTY + t * WS_STAGES + slot));
+        for (int kk = 0; kk < WS_BN / 16; ++kk) umma_ts(d_o, pcol + kk * 8, b0 + ((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(bar(L::B_V_EMPTY + t * WS_STAGES + slot));   // V slot free; also: O holds tile j (the rescale waits for it)
         if (j + 1 == nt) tc_commit(bar(L::B_O_LAST + t));
-        WS_STAMP(2, 7);
+        WS_STAMP(2, 3);
+        if (j + 2 < nt) issue_s(j + 2);
+        WS_STAMP(2, 4);
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ================================================================ softmax, one thread per query row
     const int t = warp >> 2;
@@ -384,10 +424,11 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     const float scale_log2 = p.scale * LOG2E;
     float m_ref = 0.f, l = 0.f;
     bool ok = true;
+    bool seen = false;          // lane 0: s_full of this tile was already seen complete during the previous tile
     for (int j = 0; j < nt; ++j) {
       const uint32_t tm_s = tm_lane + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
       WS_STAMP(t, 0);
-      ok = mbar_wait_warp(bar(L::B_S_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
+      if (!__shfl_sync(0xffffffffu, seen, 0)) ok = mbar_wait_warp(bar(L::B_S_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
       if (!ok) break;
       tc_fence_after();
       WS_STAMP(t, 1);
@@ -442,27 +483,49 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
         grow = true;
       }
       uint32_t pk[32];
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      float sum;
+      bool next_seen = false;   // s_full of tile j + 1 already seen complete (probed below, off the critical path)
       if (plain) {
+        // Packed FMA / ADD; every fourth pair takes the polynomial instead of the special-function unit.
+        const uint64_t sc2 = pk2(scale_log2, scale_log2), nm2 = pk2(-m_ref, -m_ref);
+        uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
         for (int i = 0; i < WS_BN; i += 2) {
-          const float a = exp2_approx(fmaf(s[i], scale_log2, -m_ref)), b = exp2_approx(fmaf(s[i + 1], scale_log2, -m_ref));
-          sum4[(i >> 1) & 3] += a + b;
-          pk[i >> 1] = pack2<T>(a, b);
+          const int q = i >> 1;
+          const uint64_t x2 = fma2(pk2(s[i], s[i + 1]), sc2, nm2);
+          float a, b;
+          if ((q & 3) == 3) {
+            exp2_poly2(x2, a, b);
+          } else {
+            float x0, x1;
+            up2(x2, x0, x1);
+            a = exp2_approx(x0);
+            b = exp2_approx(x1);
+          }
+          acc[q & 3] = add2(acc[q & 3], pk2(a, b));
+          pk[q] = pack2<T>(a, b);
+          if (q == 23 && j + 1 < nt && lane == 0)   // the answer is not needed before the next iteration begins
+            next_seen = mbar_test(bar(L::B_S_FULL + t * 2 + ((j + 1) & 1)), ((j + 1) >> 1) & 1);
         }
+        float t0, t1;
+        up2(add2(add2(acc[0], acc[1]), add2(acc[2], acc[3])), t0, t1);
+        sum = t0 + t1;
       } else {
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < WS_BN; i += 2) {
           const float a = exp2_approx(s[i] - m_ref), b = exp2_approx(s[i + 1] - m_ref);
           sum4[(i >> 1) & 3] += a + b;
           pk[i >> 1] = pack2<T>(a, b);
         }
+        sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       }
-      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      l = l * corr + sum;
       WS_STAMP(t, 5);
       if (__any_sync(0xffffffffu, grow)) {       // warp-uniform: tcgen05.ld / st are warp-wide
-        // O still receives P V of tile j - 1 (grow implies j > 0) until that tile's o_buf says otherwise
-        ok = mbar_wait_warp(bar(L::B_O_BUF + t * 2 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, p.status);
+        // O still receives P V of tile j - 1 (grow implies j > 0) until the commit behind it has arrived: the one
+        // that frees the tile's V slot
+        ok = mbar_wait_warp(bar(L::B_V_EMPTY + t * WS_STAGES + (j - 1) % WS_STAGES), ((j - 1) / WS_STAGES) & 1, p.status);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -480,6 +543,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(L::B_P_FULL + t * 2 + (j & 1)));
+      seen = next_seen;
       WS_STAMP(t, 4);
     }
     if (nt > 0) {
@@ -581,9 +645,6 @@ int launch_ws(const PrefillParams& p, const CUtensorMap& mq, const CUtensorMap& 
 #ifdef PA_DEBUG_PF_TIMING
 extern "C" int pa_debug_prefill_ws_timing(long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, g_ws_timing, sizeof(g_ws_timing)) == cudaSuccess ? 0 : 1;
-}
-extern "C" int pa_debug_prefill_ws_fine(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, g_ws_fine, sizeof(g_ws_fine)) == cudaSuccess ? 0 : 1;
 }
 #endif
 

@@ -50,6 +50,14 @@ extern "C" {
         kv_block_stride: c_int, kv_head_stride: c_int, dtype: u32, softscapping: f32,
         alibi_slopes: *const f32, kv_cache_dtype: u32, k_scale: f32, v_scale: f32, stream: i64,
     ) -> c_int;
+    /// Causal self-attention over packed prompts (the prefill branch of the layer, src/lib.rs:87-213 of the
+    /// reference crate); `cu_seqlens` is the u32 prefix-sum tensor the layer already builds.
+    pub fn paged_prefill_attention(
+        out: *mut c_void, query: *const c_void, key: *const c_void, value: *const c_void, cu_seqlens: *const u32,
+        num_seqs: c_int, total_tokens: c_int, max_seqlen: c_int, num_heads: c_int, num_kv_heads: c_int,
+        head_size: c_int, q_stride: c_int, k_stride: c_int, v_stride: c_int, out_stride: c_int, scale: f32,
+        softcapping: f32, alibi_slopes: *const f32, dtype: u32, stream: i64,
+    ) -> c_int;
     pub fn pa_paged_attention_uses_partitions(
         num_seqs: i64, num_heads: i64, num_kv_heads: i64, max_context_len: i64,
     ) -> c_int;
