@@ -208,8 +208,7 @@ struct WsLayout {
   // barrier slots (8 bytes each)
   static constexpr int B_Q_FULL = 0;
   static constexpr int B_K_FULL = 1;
-  static constexpr int B_K_EMPTY = B_K_FULL + WS_STAGES;       // [group][slot]
-  static constexpr int B_V_FULL = B_K_EMPTY + 2 * WS_STAGES;
+  static constexpr int B_V_FULL = B_K_FULL + WS_STAGES;
   static constexpr int B_V_EMPTY = B_V_FULL + WS_STAGES;       // [group][slot]
   static constexpr int B_S_FULL = B_V_EMPTY + 2 * WS_STAGES;   // [group][buffer]
   static constexpr int B_P_FULL = B_S_FULL + 4;                // [group][buffer]
@@ -304,19 +303,16 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       for (int j = 0; j < n_max && ok; ++j) {
         const int s = j % WS_STAGES;
         const uint32_t par = ((j / WS_STAGES) - 1) & 1;   // parity of the slot's previous release
-        if (j >= WS_STAGES) {                             // both groups' S of the tile this one replaces
-          if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_K_EMPTY + s), par, p.status);
-          if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_K_EMPTY + WS_STAGES + s), par, p.status);
-        }
-        if (!ok) break;
-        mbar_expect_tx(bar(L::B_K_FULL + s), L::KV_BYTES);
-        for (int db = 0; db < L::DB; ++db)
-          tma_load_3d(sK + s * L::KV_BYTES + db * (WS_BN * 128), &map_k, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_K_FULL + s));
+        // Slot s is free when both groups' P V of the tile it held is complete.  That commit also stands behind the
+        // S = Q K^T of the tile after it (issued earlier by the same thread), so it frees the K slot as well.
         if (j >= WS_STAGES) {
           if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_V_EMPTY + s), par, p.status);
           if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_V_EMPTY + WS_STAGES + s), par, p.status);
         }
         if (!ok) break;
+        mbar_expect_tx(bar(L::B_K_FULL + s), L::KV_BYTES);
+        for (int db = 0; db < L::DB; ++db)
+          tma_load_3d(sK + s * L::KV_BYTES + db * (WS_BN * 128), &map_k, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_K_FULL + s));
         mbar_expect_tx(bar(L::B_V_FULL + s), L::KV_BYTES);
         for (int db = 0; db < L::DB; ++db)
           tma_load_3d(sV + s * L::KV_BYTES + db * (WS_BN * 128), &map_v, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_V_FULL + s));
@@ -376,8 +372,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       for (int ks = 0; ks < HEAD / 16; ++ks)
         umma_ss(d, a0 + (((ks >> 2) * (WS_GROUP * 128) + (ks & 3) * 32) >> 4), b0 + (((ks >> 2) * (WS_BN * 128) + (ks & 3) * 32) >> 4),
                 IDESC_S, ks > 0);
-      tc_commit(bar(L::B_S_FULL + t * 2 + (j & 1)));
-      tc_commit(bar(L::B_K_EMPTY + t * WS_STAGES + slot));
+      tc_commit(bar(L::B_S_FULL + t * 2 + (j & 1)));   // the K slot is released by the commit behind a later P V
     };
     bool ok = nt > 0;
     if (ok) ok = wait4(bar(L::B_Q_FULL), 0, bar(L::B_K_FULL + 0), 0, true, bar(L::B_K_FULL + 1), 0, nt > 1, 0, 0, false);
@@ -390,10 +385,12 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     for (int j = 0; j < nt && ok; ++j) {
       const int slot = j % WS_STAGES;
       WS_STAMP(2, 0);
-      // P of this tile, its V, the K tile of the S that follows, and on a ragged last tile the producer's clearing
+      // P of this tile, its V, the K tile of the S that follows, and on a ragged last tile the producer's clearing:
+      // one probe instruction covers all four (a blocking wait for P alone, with the others probed first, was slower)
       ok = wait4(bar(L::B_P_FULL + t * 2 + (j & 1)), (j >> 1) & 1, bar(L::B_V_FULL + slot), (j / WS_STAGES) & 1, true,
                  bar(L::B_K_FULL + (j + 2) % WS_STAGES), ((j + 2) / WS_STAGES) & 1, j + 2 < nt, bar(L::B_V_FIXED), 0,
                  ragged && j == n_all - 1);
+      WS_STAMP(2, 1);
       if (!ok) break;
       WS_STAMP(2, 2);
       if (lane == 0) {
@@ -428,8 +425,12 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     for (int j = 0; j < nt; ++j) {
       const uint32_t tm_s = tm_lane + L::COL_S + (t * 2 + (j & 1)) * WS_BN;
       WS_STAMP(t, 0);
+#ifdef PA_DEBUG_PF_TIMING
+      if (dbg && j < 64) dbg_stamps[(t * 64 + j) * 8 + 6] = seen ? 1 : 0;
+#endif
       if (!__shfl_sync(0xffffffffu, seen, 0)) ok = mbar_wait_warp(bar(L::B_S_FULL + t * 2 + (j & 1)), (j >> 1) & 1, p.status);
       if (!ok) break;
+      WS_STAMP(t, 7);
       tc_fence_after();
       WS_STAMP(t, 1);
       float s[WS_BN];
