@@ -277,12 +277,31 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
   if (dbg_cta) for (int i = threadIdx.x; i < 3 * 64 * 8; i += blockDim.x) dbg_stamps[i] = 0;
 #endif
 
+  // Set-up, overlapped: the producer lane initialises the barriers and at once starts the loads that need no free
+  // slot (Q and the first ring-full of K / V tiles) while warp 9 obtains the tensor memory; with one CTA per SM
+  // nothing else hides this latency.
+  auto load_kv = [&](int j) {
+    const int s = j % WS_STAGES;
+    mbar_expect_tx(bar(L::B_K_FULL + s), L::KV_BYTES);
+    for (int db = 0; db < L::DB; ++db)
+      tma_load_3d(sK + s * L::KV_BYTES + db * (WS_BN * 128), &map_k, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_K_FULL + s));
+    mbar_expect_tx(bar(L::B_V_FULL + s), L::KV_BYTES);
+    for (int db = 0; db < L::DB; ++db)
+      tma_load_3d(sV + s * L::KV_BYTES + db * (WS_BN * 128), &map_v, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_V_FULL + s));
+  };
+  if (warp == 8 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    for (int i = 0; i < L::NUM_BARS; ++i) mbar_init(bar(i), (i >= L::B_P_FULL && i < L::B_P_FULL + 4) ? WS_GROUP : 1);
+    mbar_init_fence();
+    mbar_expect_tx(bar(L::B_Q_FULL), (n1 > 0 ? 2 : 1) * L::Q_BYTES);
+    for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
+      for (int db = 0; db < L::DB; ++db)
+        tma_load_3d(sQ + t * L::Q_BYTES + db * (WS_GROUP * 128), &map_q, db * 64, head, tok_lo + q0 + t * WS_GROUP, bar(L::B_Q_FULL));
+    for (int j = 0; j < n_max && j < WS_STAGES; ++j) load_kv(j);
+  }
   if (warp == 9) {
-    if (lane == 0) {
-      for (int i = 0; i < L::NUM_BARS; ++i) mbar_init(bar(i), (i >= L::B_P_FULL && i < L::B_P_FULL + 4) ? WS_GROUP : 1);
-      mbar_init_fence();
-    }
-    __syncwarp();
     tmem_alloc(smem0 + L::OFF_SLOT, L::TM_COLS);
     tmem_relinquish();
   }
@@ -295,27 +314,15 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     // ================================================================ producer
     if (lane == 0) {
       bool ok = true;
-      mbar_expect_tx(bar(L::B_Q_FULL), (n1 > 0 ? 2 : 1) * L::Q_BYTES);
-      for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
-        for (int db = 0; db < L::DB; ++db)
-          tma_load_3d(sQ + t * L::Q_BYTES + db * (WS_GROUP * 128), &map_q, db * 64, head, tok_lo + q0 + t * WS_GROUP,
-                      bar(L::B_Q_FULL));
-      for (int j = 0; j < n_max && ok; ++j) {
+      for (int j = WS_STAGES; j < n_max && ok; ++j) {
         const int s = j % WS_STAGES;
         const uint32_t par = ((j / WS_STAGES) - 1) & 1;   // parity of the slot's previous release
         // Slot s is free when both groups' P V of the tile it held is complete.  That commit also stands behind the
         // S = Q K^T of the tile after it (issued earlier by the same thread), so it frees the K slot as well.
-        if (j >= WS_STAGES) {
-          if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_V_EMPTY + s), par, p.status);
-          if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_V_EMPTY + WS_STAGES + s), par, p.status);
-        }
+        if (j - WS_STAGES < n0) ok = mbar_wait_nb(bar(L::B_V_EMPTY + s), par, p.status);
+        if (ok && j - WS_STAGES < n1) ok = mbar_wait_nb(bar(L::B_V_EMPTY + WS_STAGES + s), par, p.status);
         if (!ok) break;
-        mbar_expect_tx(bar(L::B_K_FULL + s), L::KV_BYTES);
-        for (int db = 0; db < L::DB; ++db)
-          tma_load_3d(sK + s * L::KV_BYTES + db * (WS_BN * 128), &map_k, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_K_FULL + s));
-        mbar_expect_tx(bar(L::B_V_FULL + s), L::KV_BYTES);
-        for (int db = 0; db < L::DB; ++db)
-          tma_load_3d(sV + s * L::KV_BYTES + db * (WS_BN * 128), &map_v, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_V_FULL + s));
+        load_kv(j);
       }
     }
     __syncwarp();
@@ -448,10 +455,16 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       }
       WS_STAMP(t, 2);
       const int col0 = j * WS_BN;
-      // no masked element for any row of the group, no bias: the scale is folded into the exponent's FMA
-      const bool plain = !capped && slope == 0.f && scale_log2 > 0.f && col0 + WS_BN <= q0 + t * WS_GROUP + 1 && col0 + WS_BN <= len;
+      // no bias, no soft-cap: the scale is folded into the exponent's FMA (the fast path); tiles on the diagonal or
+      // at the end of the sequence first set their masked logits to -inf, which that path turns into weights of zero
+      const bool plain = !capped && slope == 0.f && scale_log2 > 0.f;
       float mx;
       if (plain) {
+        if (!(col0 + WS_BN <= q0 + t * WS_GROUP + 1 && col0 + WS_BN <= len)) {
+#pragma unroll
+          for (int i = 0; i < WS_BN; ++i)
+            if (col0 + i >= len || col0 + i > row) s[i] = -INFINITY;
+        }
         float m8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) m8[i] = s[i];
