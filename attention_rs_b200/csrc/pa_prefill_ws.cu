@@ -43,6 +43,9 @@ constexpr int WS_BM = 2 * WS_GROUP;
 constexpr int WS_STAGES = 4;       // ring depth of K and of V
 constexpr int WS_THREADS = 352;
 constexpr float WS_RESCALE_GAP = 8.0f;
+#ifndef PA_POLY_COND
+#define PA_POLY_COND (q & 3) == 3
+#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 
@@ -508,7 +511,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
           const int q = i >> 1;
           const uint64_t x2 = fma2(pk2(s[i], s[i + 1]), sc2, nm2);
           float a, b;
-          if ((q & 3) == 3) {
+          if (PA_POLY_COND) {
             exp2_poly2(x2, a, b);
           } else {
             float x0, x1;
