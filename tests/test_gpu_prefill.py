@@ -82,3 +82,18 @@ def test_prefill_rejects_unsupported():
     q32 = torch.zeros((4, 2, 64), dtype=torch.float32, device=dev)
     with pytest.raises(pa.PagedAttentionError, match="f16 or bf16"):
         pa.prefill_attention(q32, q32, q32, cu, 4, 0.1)
+
+
+@pytest.mark.parametrize("case", range(24))
+def test_prefill_random_shapes(case):
+    """Seeded random prompt sets on the default kernels: 1-6 prompts of 1-900 tokens, MHA / GQA / MQA, every head
+    size and dtype, soft-cap or ALiBi in a third of the cases, q / k / v sliced out of wider rows in a quarter."""
+    rng = np.random.default_rng(1000 + case)
+    lens = [int(x) for x in rng.integers(1, 900, size=int(rng.integers(1, 7)))]
+    nkv = int(rng.choice([1, 2, 4]))
+    nh = nkv * int(rng.choice([1, 2, 4, 8]))
+    hs = int(rng.choice([64, 128, 128, 256]))
+    dtype = "bf16" if case % 2 == 0 else "f16"
+    softcap = 30.0 if case % 6 == 1 else 1.0
+    alibi = case % 6 == 4
+    run(lens, nh, nkv, hs, dtype, softcap=softcap, alibi=alibi, seed=2000 + case, fused_pad=3 if case % 4 == 3 else 0)
