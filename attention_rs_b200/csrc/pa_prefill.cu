@@ -295,17 +295,20 @@ extern "C" int paged_prefill_attention(void* out, const void* query, const void*
   p.status = device_status_word();
   if (!p.status) return fail(PA_ERR_CUDA, "could not set up the device status word");
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel.  PA_PREFILL_KERNEL selects another one for
+  // Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel, 256 on the single-group tcgen05 kernel (its
+  // accumulator fills tensor memory, so there is one row group per CTA).  PA_PREFILL_KERNEL selects another one for
   // them (comparison runs; read per call so that a test can switch between calls): "tcgen05_simple" or "warp_mma",
-  // the kernel head size 256 always uses.
+  // the kernel of this file.
   const char* env = std::getenv("PA_PREFILL_KERNEL");
   const bool want_warp_mma = env && std::strcmp(env, "warp_mma") == 0;
   const bool want_simple = env && std::strcmp(env, "tcgen05_simple") == 0;
   int rc = PA_ERR_UNSUPPORTED;
-  if (!want_warp_mma && (head_size == 64 || head_size == 128)) {
-    rc = want_simple ? launch_prefill_umma(p, num_seqs, head_size, dtype, s)
-                     : launch_prefill_ws(p, num_seqs, total_tokens, head_size, dtype, s);
-    if (rc == PA_ERR_UNSUPPORTED) return fail(rc, "prefill attention could not describe q / k / v to the TMA unit");
+  if (!want_warp_mma && (head_size == 64 || head_size == 128 || head_size == 256)) {
+    rc = (want_simple || head_size == 256) ? PA_ERR_UNSUPPORTED : launch_prefill_ws(p, num_seqs, total_tokens, head_size, dtype, s);
+    // The warp-specialised kernel needs tensor maps; should the driver refuse to encode them for these tensors, the
+    // single-group kernel (plain cp.async loads) computes the same thing.
+    if (rc == PA_ERR_UNSUPPORTED) rc = launch_prefill_umma(p, num_seqs, head_size, dtype, s);
+    if (rc == PA_ERR_UNSUPPORTED) return fail(rc, "prefill attention: no kernel for these tensors");
     return rc == PA_OK ? rc : fail(rc, "prefill launch failed: %s", cudaGetErrorString(cudaGetLastError()));
   }
   if (dtype == DT_BF16) {

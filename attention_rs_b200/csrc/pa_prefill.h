@@ -19,7 +19,7 @@ struct PrefillParams {
   float scale, softcap;
 };
 
-// tcgen05 / tensor-memory kernels (head sizes 64 and 128); PA_ERR_UNSUPPORTED for anything else.
+// tcgen05 / tensor-memory kernels (_ws: head sizes 64 and 128; _umma: 64, 128, 256); PA_ERR_UNSUPPORTED otherwise.
 // _ws: warp-specialised (TMA producer, MMA issuer, two softmax groups); the kernel that normally runs.
 // _umma: one row group per CTA, every thread loads and does softmax, thread 0 issues; kept as a cross-check.
 int launch_prefill_ws(const PrefillParams& p, int num_seqs, int total_tokens, int head_size, uint32_t dtype, cudaStream_t stream);

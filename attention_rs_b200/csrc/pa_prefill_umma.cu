@@ -1,7 +1,7 @@
 // Causal self-attention over packed variable-length prompts on the fifth-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory).  Same function as prefill_attention_kernel in
 // pa_prefill.cu (which restates src/lib.rs:87-213 of the reference); this is the kernel that runs for
-// head sizes 64 and 128.
+// head size 256, and for 64 / 128 on request (there the warp-specialised kernel of pa_prefill_ws.cu is the default).
 //
 // One CTA = 128 query rows of one (sequence, head); thread t owns row t, which is lane t of tensor memory.
 // Per 64-key tile:
@@ -141,11 +141,11 @@ prefill_umma_kernel(const PrefillParams p) {
   constexpr int CH = HEAD / 8;                 // 16-byte chunks per row
   constexpr int Q_BYTES = UM_BM * HEAD * 2;
   constexpr int KV_BYTES = UM_BN * HEAD * 2;
-  constexpr uint32_t TM_COLS = 256;            // power of two >= HEAD + 64 + 32; two CTAs share the SM's 512
+  constexpr uint32_t TM_COLS = HEAD <= 128 ? 256 : 512;   // power of two >= HEAD + 64 + 32; at 256 two CTAs share the SM's 512
   constexpr uint32_t COL_O = 0, COL_S = HEAD, COL_P = HEAD + UM_BN;
   constexpr uint32_t IDESC_S = instr_desc<T>(UM_BM, UM_BN, false);
   constexpr uint32_t IDESC_O = instr_desc<T>(UM_BM, HEAD, true);
-  static_assert(HEAD == 64 || HEAD == 128, "tensor-memory budget and descriptors are laid out for these head sizes");
+  static_assert(HEAD == 64 || HEAD == 128 || HEAD == 256, "tensor-memory budget and descriptors are laid out for these head sizes");
 
   const int seq = blockIdx.y, head = blockIdx.z;
   const int tok_lo = static_cast<int>(p.cu_seqlens[seq]), tok_hi = static_cast<int>(p.cu_seqlens[seq + 1]);
@@ -172,16 +172,19 @@ prefill_umma_kernel(const PrefillParams p) {
   const T* kg = reinterpret_cast<const T*>(p.k) + static_cast<int64_t>(tok_lo) * p.k_stride + kvh * HEAD;
   const T* vg = reinterpret_cast<const T*>(p.v) + static_cast<int64_t>(tok_lo) * p.v_stride + kvh * HEAD;
 
-  // Thread t copies chunk column t % CH of rows t / CH + k * (128 / CH): the column, and with it the swizzle term
-  // (rows advance by a multiple of 8), are fixed per thread, so one shared and one global offset serve every copy.
+  // Thread t copies chunk column t % CH of rows t / CH + k * (128 / CH).  The column is fixed per thread; so is the
+  // swizzle term when the rows advance by a multiple of 8 (head sizes 64 and 128), and then one shared and one global
+  // offset serve every copy.  At head size 256 the rows advance by 4 and the two alternating terms are used in turn.
   constexpr int RSTEP = UM_THREADS / CH;
   const int lr = tid / CH, lc = tid % CH;
   auto load_tile = [&](uint32_t dst, const T* src, int64_t stride, int rows, int row0, int rows_valid) {
     const uint32_t d0 = dst + tile_off(rows, lr, lc);
+    const uint32_t d1 = dst + tile_off(rows, lr + RSTEP, lc) - RSTEP * 128;   // base for odd k when RSTEP % 8 != 0
     const T* s0 = src + static_cast<int64_t>(row0 + lr) * stride + lc * 8;
 #pragma unroll
     for (int k = 0; k < rows / RSTEP; ++k)
-      cp_async16(d0 + k * (RSTEP * 128), s0 + static_cast<int64_t>(k * RSTEP) * stride, lr + k * RSTEP < rows_valid);
+      cp_async16(((RSTEP % 8 != 0) && (k & 1) ? d1 : d0) + k * (RSTEP * 128), s0 + static_cast<int64_t>(k * RSTEP) * stride,
+                 lr + k * RSTEP < rows_valid);
   };
   auto load_k = [&](int j) { load_tile(sK + (j & 1) * KV_BYTES, kg, p.k_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
   auto load_v = [&](int j) { load_tile(sV + (j & 1) * KV_BYTES, vg, p.v_stride, UM_BN, j * UM_BN, len - j * UM_BN); };
@@ -404,9 +407,11 @@ int launch_prefill_umma(const PrefillParams& p, int num_seqs, int head_size, uin
   if (dtype == DT_BF16) {
     if (head_size == 64) return launch_umma<__nv_bfloat16, 64>(p, num_seqs, stream);
     if (head_size == 128) return launch_umma<__nv_bfloat16, 128>(p, num_seqs, stream);
+    if (head_size == 256) return launch_umma<__nv_bfloat16, 256>(p, num_seqs, stream);
   } else if (dtype == DT_F16) {
     if (head_size == 64) return launch_umma<__half, 64>(p, num_seqs, stream);
     if (head_size == 128) return launch_umma<__half, 128>(p, num_seqs, stream);
+    if (head_size == 256) return launch_umma<__half, 256>(p, num_seqs, stream);
   }
   return PA_ERR_UNSUPPORTED;
 }

@@ -12,9 +12,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(params=["tcgen05", "tcgen05_simple", "warp_mma"])
 def kernel(request, monkeypatch):
-    """Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel; PA_PREFILL_KERNEL sends them to the
-    single-group tcgen05 kernel or to the warp-level MMA kernel, which head size 256 always uses.  The library
-    reads the variable per call."""
+    """Head sizes 64 and 128 run on the warp-specialised tcgen05 kernel, 256 on the single-group tcgen05 kernel;
+    PA_PREFILL_KERNEL sends every head size to the single-group kernel or to the warp-level MMA kernel.  The
+    library reads the variable per call."""
     if request.param == "tcgen05":
         monkeypatch.delenv("PA_PREFILL_KERNEL", raising=False)
     else:
