@@ -236,7 +236,9 @@ struct WsLayout {
 // a global store in front of a barrier probe delays the probe by hundreds of clocks.
 __device__ long long g_ws_timing[3 * 64 * 8];   // [role: softmax 0, softmax 1, MMA issuer 0][tile][stamp]
 #define WS_STAMP(role, k) do { if (dbg && j < 64) dbg_stamps[((role) * 64 + j) * 8 + (k)] = clock64(); } while (0)
+#define WS_MISC(k, cond) do { if (dbg_cta && (cond)) dbg_stamps[(2 * 64 + 63) * 8 + (k)] = clock64(); } while (0)
 #else
+#define WS_MISC(k, cond) do { } while (0)
 #define WS_STAMP(role, k) do { } while (0)
 #endif
 
@@ -260,7 +262,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
   const int q0 = qt * WS_BM;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef PA_DEBUG_PF_TIMING
-  const bool dbg = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 9);
+  const bool dbg = blockIdx.x == 4 && blockIdx.y == 3 && blockIdx.z == 5 && lane == 0 && (warp == 0 || warp == 4 || warp == 9);
 #endif
   const int n_all = (len + WS_BN - 1) / WS_BN;
   // key tiles each group needs (causal: up to its last row); a group whose rows all lie past the end needs none
@@ -276,7 +278,7 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
   auto bar = [&](int idx) { return smem0 + L::OFF_BAR + idx * 8; };
 #ifdef PA_DEBUG_PF_TIMING
   long long* dbg_stamps = reinterpret_cast<long long*>(smem + L::OFF_DBG);
-  const bool dbg_cta = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  const bool dbg_cta = blockIdx.x == 4 && blockIdx.y == 3 && blockIdx.z == 5;
   if (dbg_cta) for (int i = threadIdx.x; i < 3 * 64 * 8; i += blockDim.x) dbg_stamps[i] = 0;
 #endif
 
@@ -292,25 +294,32 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     for (int db = 0; db < L::DB; ++db)
       tma_load_3d(sV + s * L::KV_BYTES + db * (WS_BN * 128), &map_v, db * 64, kvh, tok_lo + j * WS_BN, bar(L::B_V_FULL + s));
   };
-  if (warp == 8 && lane == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
-    for (int i = 0; i < L::NUM_BARS; ++i) mbar_init(bar(i), (i >= L::B_P_FULL && i < L::B_P_FULL + 4) ? WS_GROUP : 1);
+  if (warp == 8) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_k)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_v)) : "memory");
+    }
+    for (int i = lane; i < L::NUM_BARS; i += 32) mbar_init(bar(i), (i >= L::B_P_FULL && i < L::B_P_FULL + 4) ? WS_GROUP : 1);
     mbar_init_fence();
-    mbar_expect_tx(bar(L::B_Q_FULL), (n1 > 0 ? 2 : 1) * L::Q_BYTES);
-    for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
-      for (int db = 0; db < L::DB; ++db)
-        tma_load_3d(sQ + t * L::Q_BYTES + db * (WS_GROUP * 128), &map_q, db * 64, head, tok_lo + q0 + t * WS_GROUP, bar(L::B_Q_FULL));
-    for (int j = 0; j < n_max && j < WS_STAGES; ++j) load_kv(j);
+    __syncwarp();
+    if (lane == 0) {
+      mbar_expect_tx(bar(L::B_Q_FULL), (n1 > 0 ? 2 : 1) * L::Q_BYTES);
+      for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t)
+        for (int db = 0; db < L::DB; ++db)
+          tma_load_3d(sQ + t * L::Q_BYTES + db * (WS_GROUP * 128), &map_q, db * 64, head, tok_lo + q0 + t * WS_GROUP, bar(L::B_Q_FULL));
+      for (int j = 0; j < n_max && j < WS_STAGES; ++j) load_kv(j);
+    }
   }
   if (warp == 9) {
     tmem_alloc(smem0 + L::OFF_SLOT, L::TM_COLS);
     tmem_relinquish();
   }
+  WS_MISC(0, tid == 0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  WS_MISC(1, tid == 0);
   const uint32_t tm_base = *reinterpret_cast<volatile uint32_t*>(smem + L::OFF_SLOT);
 
   if (warp == 8) {
@@ -563,45 +572,66 @@ prefill_ws_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
       seen = next_seen;
       WS_STAMP(t, 4);
     }
+    WS_MISC(2 + t * 3, (tid & 127) == 0);
     if (nt > 0) {
       // A barrier of its own for the end: a parity wait on o_done could be two phases behind here and pass early.
       if (ok) ok = mbar_wait_warp(bar(L::B_O_LAST + t), 0, p.status);
+      WS_MISC(3 + t * 3, (tid & 127) == 0);
       tc_fence_after();
       if (ok) {
-        // ---- normalise and store this thread's row (rows past the end only take part in the warp-wide loads)
+        // ---- normalise and store.  A thread holds a whole row, so direct stores would touch 32 lines per
+        // instruction; instead each warp stages its 32 rows in the group's Q tile (free: every S has been computed;
+        // 16-byte chunks XOR-swizzled with the row against bank conflicts) and writes them out as whole rows.
         const float inv = 1.0f / l;
-        T* og = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + row) * p.o_stride + head * HEAD;
-        const bool wide = reinterpret_cast<uintptr_t>(og) % 16 == 0;
+        const int r = tid & (WS_GROUP - 1);
+        constexpr int CPR = HEAD / 8;              // 16-byte chunks per row
+        unsigned char* stage = smem + L::OFF_Q + t * L::Q_BYTES;
+        T* obase = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(tok_lo + q0 + t * WS_GROUP) * p.o_stride + head * HEAD;
+        const bool wide = reinterpret_cast<uintptr_t>(obase) % 16 == 0 && p.o_stride % 8 == 0;   // warp-uniform
 #pragma unroll
         for (int c = 0; c < HEAD; c += 32) {
           uint32_t o[32];
           tmem_ld32(tm_o + c, o);
           tmem_ld_wait(o);
-          if (row < len) {
-            if (wide) {
+          if (wide) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 w;
-                w.x = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                w.y = pack2<T>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                w.z = pack2<T>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                w.w = pack2<T>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                *reinterpret_cast<uint4*>(og + c + i) = w;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; i += 2)
-                *reinterpret_cast<uint32_t*>(og + c + i) = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              w.y = pack2<T>(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              w.z = pack2<T>(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              w.w = pack2<T>(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              const int ch = (c + i) >> 3;
+              *reinterpret_cast<uint4*>(stage + r * (HEAD * 2) + ((ch ^ (r & 7)) << 4)) = w;
             }
+          } else if (row < len) {
+            T* og = obase + static_cast<int64_t>(r) * p.o_stride;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              *reinterpret_cast<uint32_t*>(og + c + i) = pack2<T>(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
           }
           __syncwarp();
+        }
+        if (wide) {
+          const int r_lo = (warp & 3) * 32;        // this warp's rows
+          const int valid = len - (q0 + t * WS_GROUP);   // rows of the group inside the sequence
+#pragma unroll
+          for (int k = 0; k < CPR; ++k) {
+            const int rr = r_lo + k * (32 / CPR) + lane / CPR, ch = lane % CPR;
+            if (rr < valid)
+              *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(rr) * p.o_stride + ch * 8) =
+                  *reinterpret_cast<const uint4*>(stage + rr * (HEAD * 2) + ((ch ^ (rr & 7)) << 4));
+          }
         }
       }
     }
   }
+  WS_MISC(4 + (warp >> 2) * 3, warp < 8 && (tid & 127) == 0);
   tc_fence_before();
   __syncthreads();
 #ifdef PA_DEBUG_PF_TIMING
+  if (dbg_cta && tid == 0) dbg_stamps[(2 * 64 + 63) * 8 + 7] = clock64();
+  __syncthreads();
   if (dbg_cta) for (int i = threadIdx.x; i < 3 * 64 * 8; i += blockDim.x) g_ws_timing[i] = dbg_stamps[i];
 #endif
   if (warp == 9) tmem_dealloc(tm_base, L::TM_COLS);
