@@ -330,6 +330,9 @@ class CpuPort:
         import torch
         from oracle import oracle as O
         self.O, self.w, self.np = O, w, np
+        # every host core: torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks, which is not what a CPU
+        # baseline "on all the host threads it can use" means
+        O.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
         code = {"bf16": O.BF16, "f16": O.F16, "f32": O.F32, "fp8": O.FP8}
         self.dt, self.kvdt = code[w.dtype], code[w.kv_dtype]
 

@@ -50,6 +50,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_bf16_decode.restype = ctypes.c_float
         L.oracle_bf16_decode.argtypes = [ctypes.c_uint16]
         L.oracle_max_threads.restype = ctypes.c_int
+        L.oracle_set_threads.restype = None
+        L.oracle_set_threads.argtypes = [ctypes.c_int]
         vp, i32, u32, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint32, ctypes.c_float
         L.oracle_reshape_and_cache.restype = ctypes.c_int
         L.oracle_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, u32, u32, f32, f32]
@@ -67,6 +69,11 @@ def lib() -> ctypes.CDLL:
 
 def max_threads() -> int:
     return int(lib().oracle_max_threads())
+
+
+def set_threads(n: int) -> None:
+    """Thread count of the C routines' parallel regions (overrides an OMP_NUM_THREADS a launcher exported)."""
+    lib().oracle_set_threads(int(n))
 
 
 # ---------------------------------------------------------------- dtype helpers (numpy)

@@ -151,6 +151,16 @@ int oracle_max_threads(void) {
 #endif
 }
 
+/* Thread count of the following parallel regions.  A launcher may have exported OMP_NUM_THREADS=1 for its ranks
+ * (torch.distributed.run does); the timed CPU legs of the benchmark ask for every host core instead. */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ---------------------------------------------------------------- reshape_and_cache */
 
 /*
