@@ -192,3 +192,12 @@ def test_prefill_oracle_matches_numpy_twin():
     assert np.abs(got - want).max() < 2e-6
     # the last row of a sequence attends over the whole sequence; the first only over itself
     assert np.allclose(got[0], np.repeat(O.from_storage(v, O.BF16)[0], 2, axis=0), atol=1e-6)
+
+
+def test_thread_count_can_be_set():
+    """The timed CPU legs ask for every host core even when a launcher exported OMP_NUM_THREADS=1."""
+    before = O.max_threads()
+    O.set_threads(3)
+    assert O.max_threads() == 3
+    O.set_threads(before)
+    assert O.max_threads() == before
