@@ -694,12 +694,14 @@ paged_decode_mma_kernel(const DecodeParams p) {
 // src/kernels/src/pagedattention.cu:470-566).  grid (num_heads, num_seqs), 128 threads.
 // max_logits holds log2-domain maxima, exp_sums the matching sums, tmp_out the
 // normalised partial outputs.
-template <typename T, int HEAD>
-__global__ void __launch_bounds__(128)
+// NWARP = 4 for the usual handful of partitions; 16 when a sequence has more than 64 (long contexts with few
+// sequences, where the merge grid is small and the loop over partitions is its whole run time).
+template <typename T, int HEAD, int NWARP = 4>
+__global__ void __launch_bounds__(NWARP * 32)
 paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sums, const float* __restrict__ max_logits,
                           const T* __restrict__ tmp_out, const uint32_t* __restrict__ context_lens, int max_parts,
                           int partition_size) {
-  constexpr int NWARP = 4;
+  constexpr int NT = NWARP * 32;
   // Launched as a programmatic dependent of the partition kernel: wait until that grid's results are visible.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int head = blockIdx.x, seq = blockIdx.y, num_heads = gridDim.x;
@@ -710,7 +712,7 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
   const int64_t slot0 = (static_cast<int64_t>(seq) * num_heads + head) * max_parts;
   const T* tp = tmp_out + slot0 * HEAD;
   if (nparts <= 1) {
-    for (int d = threadIdx.x; d < HEAD; d += 128) o[d] = nparts == 1 ? tp[d] : from_f32<T>(0.f);
+    for (int d = threadIdx.x; d < HEAD; d += NT) o[d] = nparts == 1 ? tp[d] : from_f32<T>(0.f);
     return;
   }
   extern __shared__ float msm[];        // [max_parts] weights, then [NWARP][HEAD] partial sums
@@ -720,14 +722,16 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
   __shared__ float red2[NWARP];
 
   float mx = -INFINITY;
-  for (int j = threadIdx.x; j < nparts; j += 128) mx = fmaxf(mx, max_logits[slot0 + j]);
+  for (int j = threadIdx.x; j < nparts; j += NT) mx = fmaxf(mx, max_logits[slot0 + j]);
 #pragma unroll
   for (int o2 = 16; o2 >= 1; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
   if (lane == 0) red[warp] = mx;
   __syncthreads();
-  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  mx = red[0];
+#pragma unroll
+  for (int w = 1; w < NWARP; ++w) mx = fmaxf(mx, red[w]);
   float sum = 0.f;
-  for (int j = threadIdx.x; j < nparts; j += 128) {
+  for (int j = threadIdx.x; j < nparts; j += NT) {
     const float e = exp_sums[slot0 + j];
     const float w = e != 0.f ? e * exp2_approx(max_logits[slot0 + j] - mx) : 0.f;   // slots folded into a neighbour
     wgt[j] = w;
@@ -737,7 +741,10 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
   for (int o2 = 16; o2 >= 1; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
   if (lane == 0) red2[warp] = sum;
   __syncthreads();
-  const float inv = 1.0f / ((red2[0] + red2[1]) + (red2[2] + red2[3]));
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < NWARP; ++w) tot += red2[w];
+  const float inv = 1.0f / tot;
 
   // Each warp sums a strided subset of the partitions; lanes cover the head dimension.
   constexpr int PER_LANE = (HEAD + 31) / 32;
@@ -769,8 +776,10 @@ paged_decode_merge_kernel(T* __restrict__ out, const float* __restrict__ exp_sum
     if (d < HEAD) part_sum[warp * HEAD + d] = a[k];
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < HEAD; d += 128) {
-    const float v = (part_sum[d] + part_sum[HEAD + d]) + (part_sum[2 * HEAD + d] + part_sum[3 * HEAD + d]);
+  for (int d = threadIdx.x; d < HEAD; d += NT) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) v += part_sum[w * HEAD + d];
     o[d] = from_f32<T>(v * inv);
   }
 }

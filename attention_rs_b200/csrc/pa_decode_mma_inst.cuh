@@ -49,20 +49,22 @@ int launch_decode_mma_nh(const DecodeParams& p, cudaStream_t stream) {
   if (partitioned) {
     // The merge is launched as a programmatic dependent: it may be scheduled while the partition grid
     // drains and waits (griddepcontrol.wait) until that grid's memory is visible.
+    const bool many = p.max_parts > 64;            // long contexts: sixteen warps share the loop over partitions
+    const int nwarp = many ? 16 : 4;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.num_heads, p.num_seqs);
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = (static_cast<size_t>(p.max_parts) + 4 * HEAD) * sizeof(float);
+    cfg.blockDim = dim3(nwarp * 32);
+    cfg.dynamicSmemBytes = (static_cast<size_t>(p.max_parts) + nwarp * HEAD) * sizeof(float);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<T, HEAD>, reinterpret_cast<T*>(p.out),
-                           static_cast<const float*>(p.exp_sums), static_cast<const float*>(p.max_logits),
-                           reinterpret_cast<const T*>(p.tmp_out), p.context_lens, p.max_parts,
-                           p.partition_size) != cudaSuccess)
+    auto kernel = many ? paged_decode_merge_kernel<T, HEAD, 16> : paged_decode_merge_kernel<T, HEAD, 4>;
+    if (cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<T*>(p.out), static_cast<const float*>(p.exp_sums),
+                           static_cast<const float*>(p.max_logits), reinterpret_cast<const T*>(p.tmp_out), p.context_lens,
+                           p.max_parts, p.partition_size) != cudaSuccess)
       return PA_ERR_CUDA;
   }
   return cudaGetLastError() == cudaSuccess ? PA_OK : PA_ERR_CUDA;
